@@ -1,0 +1,367 @@
+#!/usr/bin/env python
+"""Benchmark of the TileSpMM hot path on B200: SpMM TFLOPS = 2*nnz*colB/t (upstream src/csr2tile.h:1057).
+
+    python bench.py --gpus N --steps K --warmup W            this library (CUDA, C ABI)
+    python bench.py --impl reference ...                      CPU CSR SpMM of the checker on the host cores
+
+One "step" is one SpMM pass (all tile classes) over the resident converted matrix.  At N=1 the workload is
+benchmark configuration 2 (27-point stencil on 64^3, TF32 inputs, colB=128).  At N>1 the same stencil is
+stacked N times along z (rows = N * 262,144), the global panel sequence is cut into N shards balanced by tile
+bytes, B is broadcast once with NCCL and C stays row-partitioned: per-GPU work is fixed ("weak").
+`--workload c1|c3|c4|c5` selects another configuration (c5 = R-MAT scale 24, strong scaling of one matrix).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from tilespmm_b200 import synth  # noqa: E402
+
+PREC = {"fp16": 0, "tf32": 1}
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def make_workload(name: str, n_gpus: int, scale_override=None):
+    """CSR (float32 values), shape, config dict of one benchmark configuration."""
+    cfg = dict(synth.CONFIGS[name])
+    if name == "c2":
+        g = 64
+        if n_gpus == 1:
+            rp, ci, v, shape = synth.stencil27(g, 1002)
+        else:  # weak scaling: stack the grid along z
+            rp, ci, v, shape = stencil_stacked(g, g * n_gpus, 1002)
+        desc = f"c2: 27-point stencil {g}x{g}x{g * n_gpus}, TF32, colB=128"
+    elif name == "c1":
+        rp, ci, v, shape = synth.fixed_nnz_per_row(4096, 16, 1001)
+        desc = "c1: 4096^2, 16 nnz/row, FP16, colB=32"
+    elif name == "c3":
+        rp, ci, v, shape = synth.rmat_symmetric(scale_override or 20, 16, 1003)
+        desc = f"c3: symmetric R-MAT scale {scale_override or 20}, FP16, colB=64"
+    elif name == "c4":
+        rp, ci, v, shape = synth.mixed_density(524288, 1004)
+        desc = "c4: mixed density 524288^2, TF32, colB=256"
+    elif name == "c5":
+        rp, ci, v, shape = synth.rmat_symmetric(scale_override or 24, 16, 1005, values="u01")
+        desc = f"c5: symmetric R-MAT scale {scale_override or 24}, FP16, colB=128"
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    return rp, ci, v, shape, cfg, desc
+
+
+def stencil_stacked(g: int, gz: int, seed: int):
+    """27-point stencil on a g x g x gz grid (x fastest), same value law as configuration 2."""
+    rng = np.random.Generator(np.random.Philox(seed))
+    n = g * g * gz
+    idx = np.arange(n, dtype=np.int64)
+    x, y, z = idx % g, (idx // g) % g, idx // (g * g)
+    rows, cols, diag = [], [], []
+    for dz in (-1, 0, 1):
+        for dy in (-1, 0, 1):
+            for dx in (-1, 0, 1):
+                ok = (x + dx >= 0) & (x + dx < g) & (y + dy >= 0) & (y + dy < g) & (z + dz >= 0) & (z + dz < gz)
+                r = idx[ok]
+                rows.append(r); cols.append(r + dx + dy * g + dz * g * g)
+                diag.append(np.full(r.shape, dx == 0 and dy == 0 and dz == 0))
+    rows, cols, diag = np.concatenate(rows), np.concatenate(cols), np.concatenate(diag)
+    order = np.lexsort((cols, rows))
+    rows, cols, diag = rows[order], cols[order], diag[order]
+    vals = np.where(diag, 26.0, -1.0) + rng.uniform(-1e-3, 1e-3, size=rows.size)
+    rowptr = np.zeros(n + 1, dtype=np.int64)
+    np.add.at(rowptr, rows + 1, 1)
+    return np.cumsum(rowptr).astype(np.int32), cols.astype(np.int32), vals.astype(np.float32), (n, n)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.stop_flag, self.thread = index, [], False, None
+
+    def _loop(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def start(self):
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread:
+            self.thread.join(timeout=10)
+        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(s) > 3 + i and s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def cpu_csr_spmm_timed(prec, shape, rp, ci, vv, Bv, colB, budget_s=12.0):
+    """The CPU baseline: the checker's OpenMP CSR SpMM on all host threads, best of a few passes."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _orc
+    best, t_total, n = None, 0.0, 0
+    while n < 2 or (t_total < budget_s and n < 8):
+        t0 = time.perf_counter()
+        _orc.spmm_csr(prec, shape, rp, ci, vv, Bv, colB)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        t_total += dt
+        n += 1
+    return best, n, int(_orc.Orc.lib().orc_num_threads())
+
+
+def run_reference(args):
+    """--impl reference: upstream has no CPU SpMM (its check compares against cuSPARSE, src/main.cu:315-335), so
+    the reference arm is the checker's CPU CSR SpMM (FP32 accumulate) on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rp, ci, v, shape, cfg, desc = make_workload(args.workload, 1, args.scale)
+    prec, colB = PREC[cfg["precision"]], cfg["colB"]
+    from tilespmm_b200 import api
+    cb = api.padded_width(colB)
+    B = synth.dense_b(shape[1], cb, 1, cfg["b_dist"])
+    Bv = api.to_values(B, prec).reshape(shape[1], cb)
+    vv = api.to_values(v, prec)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _orc
+    for _ in range(args.warmup):
+        _orc.spmm_csr(prec, shape, rp, ci, vv, Bv, colB)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _orc.spmm_csr(prec, shape, rp, ci, vv, Bv, colB)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * ci.size * colB / dt / 1e12
+    threads = int(_orc.Orc.lib().orc_num_threads())
+    line = {"impl": "reference", "metric": "spmm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": cfg["precision"], "data": "synthetic", "config": {"workload": desc},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                             "sample": "whole workload, one pass per step"},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--scale", type=int, default=None, help="R-MAT scale override for c3/c5")
+    ap.add_argument("--gamma", type=float, default=None)
+    ap.add_argument("--delta", type=float, default=None)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cusparse", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    from tilespmm_b200 import api
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    rp, ci, v, shape, cfg, desc = make_workload(args.workload, world, args.scale)
+    prec, colB = PREC[cfg["precision"]], cfg["colB"]
+    cb = api.padded_width(colB)
+    vv = api.to_values(v, prec)
+    nnz = int(ci.size)
+    scaling = "weak" if args.workload == "c2" else "strong"
+
+    # threshold model (upstream src/main.cu:226-247), conversion on the GPU
+    cap = torch.cuda.get_device_capability(local)
+    feats = api.features_from_csr(rp, shape, cap[0] + cap[1] / 10.0, colB)
+    gamma, delta = api.predict(prec, feats)
+    if args.gamma is not None:
+        gamma = args.gamma
+    if args.delta is not None:
+        delta = args.delta
+    t0 = time.perf_counter()
+    m = api.TileMatrix(prec, local).convert_host(shape, rp, ci, vv, gamma, delta, shard=(rank, world))
+    torch.cuda.synchronize()
+    convert_s = time.perf_counter() - t0
+    info = m.info()
+    row0, row1 = m.row_range
+
+    # B: generated on rank 0, broadcast once over NCCL; C: this rank's row slab
+    tdt = torch.float16 if prec == 0 else torch.float32
+    if rank == 0:
+        Bh = synth.dense_b(shape[1], cb, 1, cfg["b_dist"])
+        Bh[:, colB:] = 0
+        Bv = api.to_values(Bh, prec).reshape(shape[1], cb)
+        B_pinned = torch.from_numpy(Bv.view(np.float16) if prec == 0 else Bv).pin_memory()
+        dB = B_pinned.to("cuda", non_blocking=True)
+    else:
+        Bv, B_pinned = None, None
+        dB = torch.empty((shape[1], cb), dtype=tdt, device="cuda")
+    bcast_ms = None
+    if world > 1:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        e0.record()
+        dist.broadcast(dB, src=0)
+        e1.record()
+        torch.cuda.synchronize()
+        bcast_ms = e0.elapsed_time(e1)
+    dC = torch.empty((m.c_rows(), cb), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    best_th, tune_ms = m.tune(dB, dC, cb)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(args.warmup):
+        m.spmm(dB, dC, cb, stream)
+    barrier()
+    launches0 = m.launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        m.spmm(dB, dC, cb, stream)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = m.launch_count() - launches0
+    # keep the GPU busy a little longer so that the clock sampler sees the loaded state
+    t_end = time.perf_counter() + 1.0
+    while rank == 0 and time.perf_counter() < t_end and len(sampler.samples) < 8:
+        m.spmm(dB, dC, cb, stream)
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    tflops = 2.0 * nnz * colB / (ms_step * 1e-3) / 1e12
+
+    # per-class kernel timing for the roofline of the dominant kernel (CUDA events on the launching stream)
+    cls_ms, cls_bytes = {}, {}
+    for cls in range(3):
+        if info[cls, 2] > 0:
+            cls_ms[cls] = m.time(dB, dC, cb, max(10, args.steps // 4), cls)
+            cls_bytes[cls] = m.algorithmic_bytes(cb, cls)
+    dom = max(cls_ms, key=lambda c: cls_ms[c]) if cls_ms else None
+    peak, peak_kind = measured_peak_gbs()
+    roofline = None
+    if dom is not None:
+        b3 = cls_bytes[dom]
+        ach = float(b3.sum()) / (cls_ms[dom] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": f"{api.CLASSES[dom]}-row tiles", "achieved": ach, "peak": peak, "peak_kind": peak_kind,
+                    "unit": "GB/s", "frac": ach / peak, "frac_of_nominal_8TBs": ach / 8000.0, "traffic": TRAFFIC.get((args.workload, dom)),
+                    "algorithmic_bytes": {"a_tiles": float(b3[0]), "b_gathered": float(b3[1]), "c": float(b3[2])},
+                    "kernel_ms": cls_ms[dom]}
+    all_bytes = float(m.algorithmic_bytes(cb).sum())
+
+    # end to end through the C ABI with host buffers: H2D of B, kernels, D2H of C inside the timed region
+    e2e = None
+    if rank == 0 or world > 1:
+        if B_pinned is None:
+            B_pinned = dB.cpu().pin_memory()
+        Bnp = B_pinned.numpy()
+        Ch = torch.empty((row1 - row0, cb), dtype=torch.float32).pin_memory()
+        L = api.lib()
+        import ctypes as C
+        for _ in range(2):
+            api._check(L.tsp_spmm_host(m.h, C.c_void_p(Bnp.ctypes.data), C.c_void_p(Ch.data_ptr()), cb), "tsp_spmm_host")
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            api._check(L.tsp_spmm_host(m.h, C.c_void_p(Bnp.ctypes.data), C.c_void_p(Ch.data_ptr()), cb), "tsp_spmm_host")
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": 2.0 * nnz * colB / float(dt.item()) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(Bnp.nbytes), "d2h_bytes_per_step": int(Ch.numel() * 4), "ms_per_step": float(dt.item()) * 1e3}
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if not args.no_cpu:
+        best, n, threads = cpu_csr_spmm_timed(prec, shape, rp, ci, vv, Bv, colB)
+        cpu = {"value": 2.0 * nnz * colB / best / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"whole workload, best of {n} passes ({best * 1e3:.1f} ms)"}
+    cus = None
+    if not args.no_cusparse and world == 1:
+        out3, _ = api.cusparse_baseline(prec, shape, rp, ci, vv, Bv, colB, device=local, warmup=20, repeat=100, want_c=False)
+        cus = {"time_ms": float(out3[1]), "tflops": float(out3[2]), "alg": "CUSPARSE_SPMM_ALG_DEFAULT"}
+
+    line = {"metric": "spmm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": cfg["precision"],
+            "data": "synthetic",
+            "config": {"workload": desc, "rows": int(shape[0]), "nnz": nnz, "colB": colB, "gamma": gamma, "delta": delta,
+                       "tiles_64_16_8": [int(x) for x in info[:, 3]], "best_th": [int(x) for x in best_th],
+                       "l2": "working set (A tiles + B + C) larger than L2; no flush", "convert_s": convert_s, "tune_ms": tune_ms,
+                       "broadcast_b_ms": bcast_ms},
+            "gb_per_s_algorithmic": all_bytes * world / (ms_step * 1e-3) / 1e9 if world == 1 else None,
+            "roofline": roofline, "cpu_baseline": cpu, "cusparse": cus, "clocks": clocks, "e2e": e2e,
+            "gpu_launches": int(launches)}
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
+# under profiles/ (key: workload, class); None where no capture exists.
+TRAFFIC = {}
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,129 @@
+/*
+ * tilespmm_b200 -- C ABI of the B200-native TileSpMM hot path (libtilespmm_b200.so).
+ *
+ * The upstream project (SuperScientificSoftwareLaboratory/TileSpMM) has no library API: its surface is two
+ * executables plus header-level C++ functions compiled into them.  Each entry point below replaces one of
+ * those functions; the comment above it names the upstream file:line it stands in for.  All functions
+ * return 0 on success and a positive TSP_E* code otherwise (upstream prints and exits instead,
+ * src/common.h:75-94); tsp_last_error() returns the message of the last failure on the calling thread.
+ *
+ * Conventions: precision 0 = FP16 values (IEEE binary16 bit patterns), precision 1 = TF32 (plain float,
+ * the tensor core ignores the low 13 mantissa bits exactly as in upstream, src/tilespmm_cuda.h:1118-1124).
+ * Tile classes: 0 = 64-row panels, 1 = 16-row panels, 2 = 8-row panels.  Tile widths (K extent) are
+ * 32/16/16 for FP16 and 16/8/8 for TF32 (src/main.cu:267-275).  All index arrays are 32-bit like upstream
+ * (src/common.h:34-36).  Pointers named h_* are host memory, d_* are device memory on the handle's device.
+ */
+#ifndef TILESPMM_B200_H
+#define TILESPMM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tsp_handle tsp_handle;
+
+enum
+{
+    TSP_OK = 0,
+    TSP_EINVAL = 1,    /* bad argument */
+    TSP_ECUDA = 2,     /* a CUDA call failed */
+    TSP_ENOMEM = 3,    /* host or device allocation failed */
+    TSP_ESTATE = 4,    /* call order violated (e.g. spmm before convert) */
+    TSP_EDEVICE = 5,   /* the device is not an sm_100 part */
+    TSP_ETIMEOUT = 6   /* a bounded device-side wait ran out; the kernel returned early */
+};
+
+const char *tsp_last_error(void);
+int tsp_version(void);
+
+/* ---- threshold model.  Same C ABI as upstream lib/model.so (src/ml_predict.h:8-15): 11 doubles in
+ * {unused, unused, rows, cols, nnz, sparsity, avg_row_nnz, max_row_nnz, min_row_nnz, capability, colB},
+ * (gamma, delta) out.  The decision table is re-derived for B200 and these kernels. */
+void tilespmm_predict_fp16(const double *features, float *gamma, float *delta);
+void tilespmm_predict_tf32(const double *features, float *gamma, float *delta);
+/* upstream features_from_csr (src/model_features.h:31-57); returns 0 when the CSR is inconsistent. */
+int tsp_features_from_csr(int rows, int cols, long long nnz, const int *h_rowptr, double capability, int colB,
+                          double *features11);
+
+/* ---- handle.  One handle owns one converted matrix on one device. */
+int tsp_create(tsp_handle **out, int device, int precision);
+int tsp_destroy(tsp_handle *h);
+
+/* ---- partition + conversion on the GPU: upstream matrix_split (src/hetero_split.h:144-291) followed by the
+ * three Tile_create calls (src/csr2tile.h:724-795, src/main.cu:266-275).  The CSR may be unsorted within
+ * rows and may hold repeated (row, col) entries, which are summed in value type in CSR order.
+ * shard_index/shard_count: only the panels of this shard (a contiguous range of the global panel sequence,
+ * balanced by tile bytes) are converted -- 0/1 converts everything.  The partition itself is always global,
+ * so shards of one matrix agree with the unsharded tiling. */
+int tsp_convert_host(tsp_handle *h, int rowA, int colA, long long nnz, const int *h_rowptr, const int *h_colidx,
+                     const void *h_val, float gamma, float delta, int shard_index, int shard_count);
+int tsp_convert_device(tsp_handle *h, int rowA, int colA, long long nnz, const int *d_rowptr, const int *d_colidx,
+                       const void *d_val, float gamma, float delta, int shard_index, int shard_count);
+
+/* info12[c*4 + {0,1,2,3}] = rows, nnz, panels (tilem), tiles (tilenum) of class c -- the quantities upstream
+ * prints into its CSV row (src/main.cu:306-307).  shard_rows[2] = first and one-past-last original row of
+ * the C slab this handle writes. */
+int tsp_info(const tsp_handle *h, int *info12, int *shard_rows2);
+
+/* Copies one tiling array to host memory in UPSTREAM layout (src/format.h:4-21): which = 0 orig_row[rows],
+ * 1 tile_ptr[tilem+1], 2 tile_nnz[tilenum+1], 3 tile_colidx[tilenum*BN], 4 Blockdense_Val[tilenum*BM*BN]
+ * (the device keeps 64-row tiles in tensor-core core-matrix order; the export permutes them back),
+ * 5 orig_tile_row_idx[tilem].  h_dst == NULL only queries the size.  *bytes receives the size. */
+int tsp_export(const tsp_handle *h, int cls, int which, void *h_dst, long long *bytes);
+
+/* ---- load balancing.  upstream get_optimal_prefetch_th (src/csr2tile.h:437-642) with the resource table of
+ * THESE kernels (probed with cudaFuncGetAttributes at tsp_create, the role of upstream pre/prefetch_probe.cu). */
+int tsp_top4(const tsp_handle *h, int cls, int colB_padded, int *top4);
+/* The resource row of the kernel that serves (cls, colB_padded) on this device -- what upstream's platform probe
+ * prints per kernel (pre/prefetch_probe.cu:12-28): out6 = {threads per block, registers per thread, shared bytes
+ * per block, bytes fetched per pipeline step of a block, tasks per block, column stripes per task}. */
+int tsp_kernel_info(const tsp_handle *h, int cls, int colB_padded, long long *out6);
+/* upstream tile_pretreatment + update_metadata (src/csr2tile.h:383-434, 644-711): builds the task arrays of
+ * class cls for threshold TH on the device. */
+int tsp_schedule(tsp_handle *h, int cls, int TH);
+/* Current task arrays: rows[ntasks] (bit 31 = slice of a split panel), colstart[ntasks+1]; NULL = count only. */
+int tsp_export_schedule(const tsp_handle *h, int cls, int *ntasks, unsigned int *h_rows, int *h_colstart);
+/* On-GPU threshold tuning, upstream src/csr2tile.h:964-1019: every combination of the candidate thresholds,
+ * 5 warm-up + 10 timed passes each; leaves the best schedules installed.  best3 = {th64, th16, th8}. */
+int tsp_tune(tsp_handle *h, const void *d_b, float *d_c, int colB_padded, int *best3, float *tune_ms);
+
+/* ---- SpMM.  C[rows of this shard, 0..colB_padded) = A * B with FP32 accumulation.  d_b is colA x colB_padded
+ * row-major (value type), d_c is row-major float with row stride colB_padded and at least
+ * tsp_c_rows() rows (upstream pads C to (rowA+64)/64*64 rows, src/csr2tile.h:835-842).  Unlike upstream
+ * (src/csr2tile.h:1024) the caller does not have to clear C: panels without tiles are written as zeros and
+ * the rows of split panels are cleared by a kernel of this call.  stream is a cudaStream_t (NULL = legacy). */
+int tsp_spmm(tsp_handle *h, const void *d_b, float *d_c, int colB_padded, void *stream);
+long long tsp_c_rows(const tsp_handle *h);
+/* Same, with host buffers: copies B to the device, runs, copies the first rowA rows of C back
+ * (upstream src/csr2tile.h:839-842, 1020-1032). */
+int tsp_spmm_host(tsp_handle *h, const void *h_b, float *h_c, int colB_padded);
+
+/* Kernel launches issued by tsp_spmm so far (all classes, including the clearing kernel). */
+long long tsp_launch_count(const tsp_handle *h);
+/* Algorithmic bytes of one SpMM in the upstream tile format: bytes3 = {A tiles + column indices, gathered B
+ * rows, C}; per class when cls >= 0, all classes when cls < 0. */
+int tsp_algorithmic_bytes(const tsp_handle *h, int cls, int colB_padded, double *bytes3);
+/* Times `iters` passes of one class kernel alone (cls 0..2) or of the whole SpMM (cls < 0) with CUDA events
+ * on the launching stream; ms = mean per pass. */
+int tsp_time(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB_padded, int iters, float *ms);
+
+/* ---- the upstream runtime driver call_tilespmm_cuda (src/csr2tile.h:826-1093): upload, threshold candidates,
+ * warm-up, tuning, checked run (h_c receives rowA x colB_padded floats, may be NULL), timed loop of `repeat`
+ * passes.  out6 = {best_th64, best_th16, best_th8, pre_time_ms (cpu_pre_time_ms + candidate + tuning time),
+ * time_ms, tflops = 2*nnz*colB_logical/time}. */
+int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB_padded, int colB_logical, double cpu_pre_time_ms,
+            int repeat, double *out6);
+
+/* ---- the cuSPARSE baseline upstream runs next to its own kernels, cusparse_spmm_all (src/main.cu:16-134):
+ * CSR, CUSPARSE_SPMM_ALG_DEFAULT, FP32 compute; FP16 inputs for precision 0 and true FP32 inputs for
+ * precision 1.  h_c is m x n floats (may be NULL).  out3 = {pre_time_ms, time_ms, tflops}. */
+int tsp_cusparse_baseline(int device, int precision, int m, int k, long long nnz, const int *h_rowptr,
+                          const int *h_colidx, const void *h_val, int n, int ldb, const void *h_b, float *h_c,
+                          int warmup, int repeat, double *out3);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -355,6 +355,10 @@ typedef struct
     long long shared_bytes_per_sm;
     int threads, registers_per_thread, iteration_bytes;
     long long shared_bytes;
+    /* launch geometry of the kernel: tasks served by one block and column stripes per task.  Upstream:
+     * 4 tasks per block for the 32-column 8/16-row kernels, else 1; ceil(colB/64) stripes, 1 when colB == 32
+     * (src/csr2tile.h:590-601). */
+    int tasks_per_block, stripes;
 } OrcResources;
 
 /* Upstream get_optimal_prefetch_th (src/csr2tile.h:437-642); float arithmetic in upstream's order. */
@@ -428,9 +432,7 @@ int orc_top4(const OrcTiles *T, int cls, int colB, const OrcResources *R, int *t
         }
         if (tasks == prev_tasks) continue; /* src/csr2tile.h:586-588 */
         prev_tasks = tasks;
-        long long blocks;
-        if (colB == 32) blocks = (BM == 8 || BM == 16) ? (tasks + 3) / 4 : tasks;
-        else blocks = tasks * ((colB + 63) / 64);
+        long long blocks = (tasks * R->stripes + R->tasks_per_block - 1) / R->tasks_per_block;
         float cost_base = (float)blocks / cap * TH;
         float cost_tail = (float)max_chunk;
         float cost_l2 = l2_penalty * lambda_l2;

@@ -32,7 +32,7 @@ class OrcResources(C.Structure):
     _fields_ = [("sm_count", C.c_int), ("threads_per_sm", C.c_int), ("blocks_per_sm", C.c_int),
                 ("registers_per_sm", C.c_int), ("l2_bytes", C.c_int), ("shared_bytes_per_sm", C.c_longlong),
                 ("threads", C.c_int), ("registers_per_thread", C.c_int), ("iteration_bytes", C.c_int),
-                ("shared_bytes", C.c_longlong)]
+                ("shared_bytes", C.c_longlong), ("tasks_per_block", C.c_int), ("stripes", C.c_int)]
 
 
 # rows of the upstream kernel table compiled into oracle/_ref (oracle/make_prefetch_stub.sh):
@@ -49,7 +49,9 @@ B200_L2 = 132644864
 def upstream_resources(precision, cls, colB_padded, l2_bytes=B200_L2):
     group = {0: 2, 1: 1, 2: 0}[cls]
     th, regs, smem, itb = UPSTREAM_KERNELS[precision][group * 2 + (colB_padded != 32)]
-    return OrcResources(148, 2048, 32, 65536, l2_bytes, 233472, th, regs, itb, smem)
+    tpb = 4 if (colB_padded == 32 and cls != 0) else 1
+    stripes = 1 if colB_padded == 32 else (colB_padded + 63) // 64
+    return OrcResources(148, 2048, 32, 65536, l2_bytes, 233472, th, regs, itb, smem, tpb, stripes)
 
 
 class _Tiles:

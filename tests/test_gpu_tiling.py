@@ -1,0 +1,104 @@
+"""GPU parity tests (through the C ABI): the GPU partitioning + conversion must be BIT-EXACT against the
+checker (the C restatement pinned to upstream, and the golden digests made by upstream itself)."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+import _orc
+import cases
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "tiling_golden.json")))
+CASES = cases.small_cases()
+
+
+def h(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()[:16]
+
+
+def digest(m):
+    return {f"{_orc.CLASSES[c]}:{w}": h(m.array(c, w)) for c in range(3) for w in _orc.ARRAYS}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+@pytest.mark.parametrize("prec", [0, 1])
+def test_tiling_bit_exact_vs_upstream_golden(name, prec):
+    from tilespmm_b200 import api
+    rp, ci, v, shape = CASES[name]
+    m = api.TileMatrix(prec)
+    for (g, d) in cases.GAMMA_DELTA:
+        rec = GOLDEN["tiling"][f"{name}|{prec}|{g}|{d}"]
+        m.convert_host(shape, rp, ci, v, g, d)
+        assert m.info().tolist() == rec["info"], (name, prec, g, d)
+        got = digest(m)
+        if got != rec["arrays"]:   # show the first differing array element by element
+            o = _orc.Orc(prec, shape, rp, ci, v, g, d)
+            for c in range(3):
+                for w in _orc.ARRAYS:
+                    np.testing.assert_array_equal(m.array(c, w), o.array(c, w), err_msg=f"{name} prec={prec} g={g} d={d} cls={c} {w}")
+        assert got == rec["arrays"]
+        for cls in range(3):
+            for TH in (8, 24, 64):
+                rows, cs = m.schedule(cls, TH)
+                assert [int(rows.size), h(rows), h(cs)] == rec["sched"][f"{cls}:{TH}"], (name, prec, g, d, cls, TH)
+    m.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_threshold_candidates_match_cost_model(prec):
+    """tsp_top4 against the checker's cost model fed with the resource rows of THESE kernels."""
+    from tilespmm_b200 import api
+    import torch
+    props = torch.cuda.get_device_properties(0)
+    for name in ("rmat_s11", "stencil_g17", "banded_4099", "rand_wide_64x5000"):
+        rp, ci, v, shape = CASES[name]
+        for (g, d) in ((2.0, 1.2), (0.0, 1.5), (5.0, 0.0), (5.0, 3.0)):
+            m = api.TileMatrix(prec).convert_host(shape, rp, ci, v, g, d)
+            o = _orc.Orc(prec, shape, rp, ci, v, g, d)
+            for cls in range(3):
+                for cb in (32, 64, 128, 256):
+                    k = m.kernel_info(cls, cb)
+                    res = _orc.OrcResources(props.multi_processor_count, props.max_threads_per_multi_processor, 32,
+                                            props.regs_per_multiprocessor, props.L2_cache_size, props.shared_memory_per_multiprocessor,
+                                            int(k[0]), int(k[1]), int(k[3]), int(k[2]), int(k[4]), int(k[5]))
+                    assert m.top4(cls, cb).tolist() == o.top4(cls, cb, res).tolist(), (name, g, d, cls, cb)
+            m.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_larger_seeded_inputs_vs_checker(prec):
+    """Benchmark-shaped inputs at sizes the CPU checker converts in seconds."""
+    from tilespmm_b200 import api, synth
+    inputs = [synth.stencil27(40, 1002), synth.rmat_symmetric(16, 16, 1003), synth.mixed_density(65536, 1004),
+              synth.fixed_nnz_per_row(4096, 16, 1001)]
+    m = api.TileMatrix(prec)
+    for rp, ci, v, shape in inputs:
+        for (g, d) in ((2.0, 1.2), (1.4, 1.5), (0.0, 1.5), (5.0, 0.0), (5.0, 3.0)):
+            m.convert_host(shape, rp, ci, v, g, d)
+            o = _orc.Orc(prec, shape, rp, ci, v, g, d)
+            assert m.info().tolist() == o.info().tolist()
+            assert digest(m) == o.digest(), (shape, g, d)
+    m.close()
+
+
+def test_shards_agree_with_unsharded_tiling():
+    """Sharding cuts the global panel sequence: concatenating the shards' arrays gives the unsharded arrays."""
+    from tilespmm_b200 import api, synth
+    rp, ci, v, shape = synth.rmat_symmetric(14, 16, 77)
+    for prec, (g, d) in ((0, (2.0, 1.2)), (1, (5.0, 3.0)), (0, (0.0, 1.5))):
+        full = api.TileMatrix(prec).convert_host(shape, rp, ci, v, g, d)
+        full.info()
+        parts = [api.TileMatrix(prec).convert_host(shape, rp, ci, v, g, d, shard=(k, 3)) for k in range(3)]
+        infos = [p.info() for p in parts]
+        assert sum(i[:, 3] for i in infos).tolist() == full.info()[:, 3].tolist()
+        assert sum(i[:, 0] for i in infos).tolist() == full.info()[:, 0].tolist()
+        assert parts[0].row_range[0] == 0 and parts[-1].row_range[1] == shape[0]
+        for a, b in zip(parts[:-1], parts[1:]):
+            assert a.row_range[1] == b.row_range[0]
+        for cls in range(3):
+            for w in ("tile_colidx", "tile_val", "panel_row", "orig_row"):
+                np.testing.assert_array_equal(np.concatenate([p.array(cls, w) for p in parts]), full.array(cls, w))

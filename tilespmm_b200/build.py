@@ -1,0 +1,57 @@
+"""Builds libtilespmm_b200.so (hand-written CUDA for sm_100a behind a C ABI) in-tree with nvcc."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libtilespmm_b200.so")
+SOURCES = ["api.cu", "convert.cu", "sched.cu", "spmm_small.cu", "spmm64.cu", "model.cu"]
+NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-w"]
+
+
+def _newer(target: str, deps: list[str]) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(d) <= t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every translation unit to an object and links the shared library.  Returns its path."""
+    nvcc = os.environ.get("NVCC", "nvcc")
+    headers = [os.path.join(CSRC, "tsp_internal.cuh"), os.path.join(HERE, "..", "include", "tilespmm_b200.h")]
+    objs = []
+    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    procs = []
+    for src in SOURCES:
+        s = os.path.join(CSRC, src)
+        o = os.path.join(HERE, "build", src.replace(".cu", ".o"))
+        objs.append(o)
+        if not force and _newer(o, [s] + headers):
+            continue
+        cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    logs = []
+    for src, p in procs:
+        out, _ = p.communicate()
+        logs.append(f"== {src}\n{out}")
+        if p.returncode != 0:
+            sys.stderr.write(out)
+            raise RuntimeError(f"nvcc failed on {src}")
+    if procs or not os.path.exists(LIB) or force:
+        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcusparse", "-lcudart"]
+        subprocess.run(cmd, check=True)
+    if logs:
+        with open(os.path.join(HERE, "build", "ptxas.log"), "w") as fh:
+            fh.write("\n".join(logs))
+        if verbose:
+            print("\n".join(logs))
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

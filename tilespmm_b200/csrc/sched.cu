@@ -1,0 +1,211 @@
+// Load balancing: threshold candidates from the cost model and the task arrays for one threshold.
+//
+// Replaces upstream get_optimal_prefetch_th (src/csr2tile.h:437-642), tile_pretreatment (src/csr2tile.h:383-434)
+// and update_metadata (src/csr2tile.h:644-711).  The task arrays are built on the device from tile_ptr
+// (upstream: host loop + upload per tuning combination); the cost model runs on the host over the histogram
+// of tiles per panel, in float and in upstream's evaluation order, with the resource rows of THESE kernels.
+#include <cub/cub.cuh>
+#include <math.h>
+
+#include "tsp_internal.cuh"
+
+void tsp_small_resources(int precision, int cls, int colB, TspKernelResources *out);
+void tsp_class64_resources(int precision, int colB, TspKernelResources *out);
+
+void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out)
+{
+    if (cls == 0) tsp_class64_resources(precision, colB, out);
+    else tsp_small_resources(precision, cls, colB, out);
+}
+
+namespace
+{
+
+__global__ void k_task_counts(int tilem, const int *__restrict__ tile_ptr, int TH, int *__restrict__ counts)
+{
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p > tilem) return;
+    if (p == tilem) { counts[p] = 0; return; }
+    const int len = tile_ptr[p + 1] - tile_ptr[p];
+    counts[p] = len <= TH ? 1 : (len + TH - 1) / TH;  // src/csr2tile.h:392-396
+}
+
+__global__ void k_task_fill(int tilem, const int *__restrict__ tile_ptr, const int *__restrict__ panel_row, int TH,
+                            const int *__restrict__ task_base, unsigned int *__restrict__ task_row, int *__restrict__ task_start,
+                            int *__restrict__ split_row, int *__restrict__ split_count)
+{
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= tilem) return;
+    const int t0 = tile_ptr[p], len = tile_ptr[p + 1] - t0, b = task_base[p], row = panel_row[p];
+    if (p == 0) task_start[0] = t0;
+    if (len <= TH)
+    {
+        task_row[b] = (unsigned int)row;
+        task_start[b + 1] = t0 + len;
+        return;
+    }
+    const int parts = (len + TH - 1) / TH, each = (len + parts - 1) / parts;  // src/csr2tile.h:421-422
+    for (int s = 0; s < parts; s++)
+    {
+        task_row[b + s] = (unsigned int)row | 0x80000000u;
+        task_start[b + s + 1] = s == parts - 1 ? t0 + len : t0 + (s + 1) * each;
+    }
+    split_row[atomicAdd(split_count, 1)] = row;
+}
+
+}  // namespace
+
+int tsp_schedule(tsp_handle *h, int cls, int TH)
+{
+    if (!h || cls < 0 || cls > 2 || TH <= 0) { tsp_set_error("schedule: bad argument"); return TSP_EINVAL; }
+    if (!h->converted) { tsp_set_error("schedule: convert first"); return TSP_ESTATE; }
+    TSP_CUDA(cudaSetDevice(h->device));
+    TspClass &c = h->cls[cls];
+    c.TH = TH; c.ntasks = 0; c.nsplit = 0;
+    if (c.tilem == 0) return TSP_OK;
+    if (!c.d_task_count)
+    {
+        TSP_CUDA(cudaMalloc((void **)&c.d_task_count, ((size_t)c.tilem + 2) * 4));
+        TSP_CUDA(cudaMalloc((void **)&c.d_split_row, ((size_t)c.tilem + 1) * 4));
+    }
+    const int T = 256;
+    k_task_counts<<<(c.tilem + 1 + T - 1) / T, T>>>(c.tilem, c.d_tile_ptr, TH, c.d_task_count);
+    TSP_CUDA(cudaGetLastError());
+    size_t bytes = 0;
+    TSP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, c.d_task_count, c.d_task_count, c.tilem + 1));
+    void *scratch = nullptr;
+    TSP_CUDA(cudaMalloc(&scratch, bytes ? bytes : 1));
+    cudaError_t e = cub::DeviceScan::ExclusiveSum(scratch, bytes, c.d_task_count, c.d_task_count, c.tilem + 1);
+    int ntasks = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&ntasks, c.d_task_count + c.tilem, 4, cudaMemcpyDeviceToHost);
+    cudaFree(scratch);
+    TSP_CUDA(e);
+    if ((long long)ntasks > c.cap_tasks)
+    {
+        cudaFree(c.d_task_row); cudaFree(c.d_task_start);
+        c.d_task_row = nullptr; c.d_task_start = nullptr;
+        c.cap_tasks = (long long)ntasks + ntasks / 4 + 16;
+        TSP_CUDA(cudaMalloc((void **)&c.d_task_row, (size_t)c.cap_tasks * 4));
+        TSP_CUDA(cudaMalloc((void **)&c.d_task_start, ((size_t)c.cap_tasks + 1) * 4));
+    }
+    int *d_split_count = c.d_task_count + c.tilem + 1;
+    TSP_CUDA(cudaMemset(d_split_count, 0, 4));
+    k_task_fill<<<(c.tilem + T - 1) / T, T>>>(c.tilem, c.d_tile_ptr, c.d_panel_row, TH, c.d_task_count, c.d_task_row, c.d_task_start,
+                                             c.d_split_row, d_split_count);
+    TSP_CUDA(cudaGetLastError());
+    TSP_CUDA(cudaMemcpy(&c.nsplit, d_split_count, 4, cudaMemcpyDeviceToHost));
+    c.ntasks = ntasks;
+    return TSP_OK;
+}
+
+int tsp_export_schedule(const tsp_handle *h, int cls, int *ntasks, unsigned int *h_rows, int *h_colstart)
+{
+    if (!h || cls < 0 || cls > 2 || !ntasks) { tsp_set_error("export_schedule: bad argument"); return TSP_EINVAL; }
+    const TspClass &c = h->cls[cls];
+    *ntasks = c.ntasks;
+    if (c.ntasks == 0) return TSP_OK;
+    if (h_rows) TSP_CUDA(cudaMemcpy(h_rows, c.d_task_row, (size_t)c.ntasks * 4, cudaMemcpyDeviceToHost));
+    if (h_colstart) TSP_CUDA(cudaMemcpy(h_colstart, c.d_task_start, ((size_t)c.ntasks + 1) * 4, cudaMemcpyDeviceToHost));
+    return TSP_OK;
+}
+
+// The four cheapest thresholds under the upstream cost model (src/csr2tile.h:437-642).
+int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
+{
+    if (!h || cls < 0 || cls > 2 || !top4 || colB <= 0) { tsp_set_error("top4: bad argument"); return TSP_EINVAL; }
+    if (!h->converted) { tsp_set_error("top4: convert first"); return TSP_ESTATE; }
+    for (int i = 0; i < 4; i++) top4[i] = 32;
+    const TspClass &c = h->cls[cls];
+    if (c.tilenum == 0) return TSP_OK;
+    TspKernelResources R;
+    tsp_kernel_resources(h->precision, cls, colB, &R);
+    const int is_tf32 = h->precision, BM = c.BM;
+    const int sm = h->prop.multiProcessorCount;
+    int blk_reg = h->prop.regsPerMultiprocessor / (R.registers_per_thread > 0 ? R.registers_per_thread * R.threads : 1);
+    int blk_smem = R.shared_bytes > 0 ? (int)(h->prop.sharedMemPerMultiprocessor / (size_t)R.shared_bytes) : h->prop.maxBlocksPerMultiProcessor;
+    int blk_sm = h->prop.maxThreadsPerMultiProcessor / R.threads;
+    if (blk_reg < blk_sm) blk_sm = blk_reg;
+    if (blk_smem < blk_sm) blk_sm = blk_smem;
+    if (blk_sm > h->prop.maxBlocksPerMultiProcessor) blk_sm = h->prop.maxBlocksPerMultiProcessor;
+    if (blk_sm <= 0) { tsp_set_error("top4: the kernel does not fit this GPU"); return TSP_EDEVICE; }
+    const float cap = (float)(blk_sm * sm);
+    const float lambda_l2 = (float)(R.iteration_bytes * cap) / (float)h->prop.l2CacheSize;
+    // weight of one atomic slice; the table is upstream's (src/csr2tile.h:484-495)
+    float lambda_atom = 0.01f;
+    if (colB == 32)
+    {
+        if (BM == 64) lambda_atom = is_tf32 ? 0.020f : 0.019f;
+        else if (BM == 16) lambda_atom = is_tf32 ? 0.00830f : 0.00844f;
+        else lambda_atom = is_tf32 ? 0.00674f : 0.00360f;
+    }
+    else
+    {
+        if (BM == 16) lambda_atom = is_tf32 ? 0.01048f : 0.01163f;
+        else if (BM == 8) lambda_atom = is_tf32 ? 0.00960f : 0.00826f;
+    }
+    const float atom_per_col = lambda_atom * (1.0f / 32.0f);
+
+    const std::vector<int> &tp = c.h_tile_ptr;
+    int max_len = 0;
+    long long total_len = 0;
+    for (int p = 0; p < c.tilem; p++)
+    {
+        const int len = tp[p + 1] - tp[p];
+        if (len > max_len) max_len = len;
+        total_len += len;
+    }
+    if (max_len == 0) return TSP_OK;
+    std::vector<int> hist((size_t)max_len + 1, 0);
+    for (int p = 0; p < c.tilem; p++) hist[tp[p + 1] - tp[p]]++;
+    hist[0] = 0;
+    std::vector<int> lens;
+    for (int len = 1; len <= max_len; len++) if (hist[len]) lens.push_back(len);
+
+    const float avg_len = (float)total_len / c.tilem;
+    float atom_pen = atom_per_col * (float)colB;
+    if (max_len > avg_len * 5.0f) atom_pen *= 0.04f;
+    int tmax = (max_len + 7) / 8 * 8;
+    if (tmax > 128) tmax = 128;
+    // one block of these kernels serves tasks_per_block tasks of one stripe
+    const int stripe = cls == 0 ? (colB == 32 ? 32 : (colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64)))
+                                : (colB == 32 ? 32 : (colB % 128 == 0 ? 128 : 64));
+    int cand_th[16], ncand = 0;
+    float cand_cost[16];
+    long long prev_tasks = -1;
+    for (int TH = 8; TH <= tmax; TH += 8)
+    {
+        long long atom_ops = 0, tasks = 0;
+        int max_chunk = 0;
+        float l2_penalty = 0.0f;
+        for (int len : lens)
+        {
+            const int cnt = hist[len];
+            const int parts = (len + TH - 1) / TH, each = (len + parts - 1) / parts;
+            atom_ops += (long long)(parts - 1) * cnt;
+            tasks += (long long)parts * cnt;
+            if (each > max_chunk) max_chunk = each;
+            if (parts > 1) l2_penalty += (1.0f - (1.0f / (float)parts)) * cnt;
+        }
+        if (tasks == prev_tasks) continue;
+        prev_tasks = tasks;
+        const long long blocks = (tasks * (colB / stripe) + R.tasks_per_block - 1) / R.tasks_per_block;
+        const float cost_base = (float)blocks / cap * TH;
+        const float cost_tail = (float)max_chunk;
+        const float cost_l2 = l2_penalty * lambda_l2;
+        const float cost_comp = cost_base + cost_tail + cost_l2;
+        const float cost_atom = atom_pen * atom_ops;
+        cand_th[ncand] = TH;
+        cand_cost[ncand] = cost_comp + cost_atom;
+        ncand++;
+    }
+    for (int i = 1; i < ncand; i++)  // stable: ties keep ascending TH (src/csr2tile.h:620-631)
+    {
+        const int th = cand_th[i];
+        const float cost = cand_cost[i];
+        int j = i - 1;
+        while (j >= 0 && cand_cost[j] > cost) { cand_th[j + 1] = cand_th[j]; cand_cost[j + 1] = cand_cost[j]; j--; }
+        cand_th[j + 1] = th; cand_cost[j + 1] = cost;
+    }
+    for (int i = 0; i < 4; i++) top4[i] = i < ncand ? cand_th[i] : cand_th[0];
+    return TSP_OK;
+}

@@ -1,0 +1,323 @@
+// SpMM kernels for the 16-row and 8-row tile classes: warp-level mma.sync with a multi-stage cp.async ring.
+//
+// They replace upstream stir_spmm_cuda_kernel_v16*/v8* (src/tilespmm_cuda.h:12-1023) and the launch switches
+// (src/tilespmm_cuda.h:1634-1708).  Differences that matter on B200:
+//   * one warp owns one (task, column stripe) and keeps a STAGES-deep ring of gathered B rows in flight
+//     (upstream: depth 1 for 16-row tiles, none for 8-row tiles), so that the gather is limited by memory
+//     throughput, not by latency;
+//   * a stripe is up to 128 columns wide (upstream: 64), so the A tile and the column indices are read
+//     once per 128 columns and a gathered row segment is up to 512 contiguous bytes;
+//   * every global access is a 16-byte cp.async (B rows, A tile) or a full 32-byte sector store (C);
+//   * shared-memory rows are XOR-swizzled in 16-byte chunks so that ldmatrix reads are conflict-free.
+// Tile values are consumed in the upstream fragment order (src/csr2tile.h:255-307): one 16-byte (16-row) or
+// 8-byte (8-row) load per lane is the MMA operand.
+#include "tsp_internal.cuh"
+
+namespace
+{
+
+constexpr int STAGES = 4;
+constexpr int WARPS = 4;
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *smem)
+{
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_f16(float *d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_tf32(float *d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int PREC, int CLS, int NS>
+struct SmallCfg
+{
+    static constexpr int SZ = PREC == 0 ? 2 : 4;
+    static constexpr int BM = CLS == 1 ? 16 : 8;
+    static constexpr int BN = PREC == 0 ? 16 : 8;
+    static constexpr int RB = NS * SZ;                 // bytes of one gathered row segment
+    static constexpr int CPR = RB / 16;                // 16-byte chunks per row
+    static constexpr int A_BYTES = BM * BN * SZ;       // 512 (16-row) or 256 (8-row)
+    static constexpr int B_BYTES = BN * RB;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SMEM = WARPS * WARP_BYTES;
+};
+
+// chunk position of 16-byte chunk c of row k inside its shared-memory row
+template <int RB>
+__device__ __forceinline__ int swz(int c, int k)
+{
+    if (RB >= 128) return c ^ (k & 7);
+    return c ^ ((k >> 1) & 3);
+}
+
+template <int PREC, int CLS, int NS>
+__global__ void __launch_bounds__(WARPS * 32)
+k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const unsigned int *__restrict__ task_row,
+             const int *__restrict__ task_start, const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
+             const unsigned char *__restrict__ dB, float *__restrict__ dC)
+{
+    using Cfg = SmallCfg<PREC, CLS, NS>;
+    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * WARPS + warp;
+    if (unit >= (long long)ntasks * nstripes) return;
+    const int task = (int)(unit / nstripes), stripe = (int)(unit - (long long)task * nstripes);
+    unsigned char *ring = smem_raw + warp * Cfg::WARP_BYTES;
+
+    const unsigned int trow = task_row[task];
+    const bool split = (trow >> 31) != 0;
+    const int first_row = (int)(trow & 0x7fffffffu) - row_begin;
+    const int t0 = task_start[task], nt = task_start[task + 1] - t0;
+    const size_t stripe_bytes = (size_t)stripe * NS * SZ;
+    const size_t ldb_bytes = (size_t)ldb * SZ;
+
+    constexpr int NACC = CLS == 1 ? NS / 8 : NS / 16;
+    float acc[NACC][4];
+#pragma unroll
+    for (int i = 0; i < NACC; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
+
+    // column index of tile row `lane` for the tile that will be issued next
+    int idx_next = (nt > 0 && lane < BN) ? __ldg(tile_colidx + (size_t)t0 * BN + lane) : 0;
+
+    auto issue = [&](int i) {
+        unsigned char *st = ring + (i % STAGES) * Cfg::STAGE_BYTES;
+        const unsigned char *a_src = tile_val + (size_t)(t0 + i) * Cfg::A_BYTES;
+        if (lane * 16 < Cfg::A_BYTES) cp_async16(st + lane * 16, a_src + lane * 16);
+        const int idx_mine = idx_next;
+#pragma unroll
+        for (int it = 0; it < (BN * CPR + 31) / 32; it++)
+        {
+            const int q = it * 32 + lane;
+            const int k = q / CPR, c = q % CPR;
+            const int col = __shfl_sync(0xffffffffu, idx_mine, k & (BN - 1));
+            if (q < BN * CPR)
+                cp_async16(st + Cfg::A_BYTES + k * RB + swz<RB>(c, k) * 16, dB + (size_t)col * ldb_bytes + stripe_bytes + c * 16);
+        }
+        if (i + 1 < nt && lane < BN) idx_next = __ldg(tile_colidx + (size_t)(t0 + i + 1) * BN + lane);
+    };
+
+    for (int i = 0; i < STAGES - 1; i++)
+    {
+        if (i < nt) issue(i);
+        cp_async_commit();
+    }
+    for (int i = 0; i < nt; i++)
+    {
+        if (i + STAGES - 1 < nt) issue(i + STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        const unsigned char *st = ring + (i % STAGES) * Cfg::STAGE_BYTES;
+        const unsigned char *sb = st + Cfg::A_BYTES;
+        if constexpr (CLS == 1 && PREC == 0)
+        {
+            const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
+            const int k = ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int nb = 0; nb < NS / 8; nb += 2)
+            {
+                const int chunk = nb + (lane >> 4);
+                unsigned r0, r1, r2, r3;
+                ldmatrix_x4_trans(r0, r1, r2, r3, sb + k * RB + swz<RB>(chunk, k) * 16);
+                mma_f16(acc[nb], a.x, a.y, a.z, a.w, r0, r1);
+                mma_f16(acc[nb + 1], a.x, a.y, a.z, a.w, r2, r3);
+            }
+        }
+        else if constexpr (CLS == 1 && PREC == 1)
+        {
+            const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
+            const int k = lane & 3, n = lane >> 2;
+#pragma unroll
+            for (int nb = 0; nb < NS / 8; nb++)
+            {
+                const int chunk = nb * 2 + (n >> 2);
+                const unsigned b0 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(chunk, k) * 16 + (n & 3) * 4);
+                const unsigned b1 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16 + (n & 3) * 4);
+                mma_tf32(acc[nb], a.x, a.y, a.z, a.w, b0, b1);
+            }
+        }
+        else if constexpr (CLS == 2 && PREC == 0)
+        {
+            const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
+            const int k = (lane >> 4) * 8 + (lane & 7);
+#pragma unroll
+            for (int mb = 0; mb < NS / 16; mb++)
+            {
+                const int chunk = mb * 2 + ((lane >> 3) & 1);
+                unsigned a0, a1, a2, a3;
+                ldmatrix_x4_trans(a0, a1, a2, a3, sb + k * RB + swz<RB>(chunk, k) * 16);
+                mma_f16(acc[mb], a0, a1, a2, a3, b.x, b.y);
+            }
+        }
+        else
+        {
+            const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
+            const int k = lane & 3, m = lane >> 2;
+#pragma unroll
+            for (int mb = 0; mb < NS / 16; mb++)
+            {
+                const int c0 = mb * 4 + (m >> 2), c1 = c0 + 2;
+                const unsigned a0 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(c0, k) * 16 + (m & 3) * 4);
+                const unsigned a1 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(c1, k) * 16 + (m & 3) * 4);
+                const unsigned a2 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(c0, k + 4) * 16 + (m & 3) * 4);
+                const unsigned a3 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(c1, k + 4) * 16 + (m & 3) * 4);
+                mma_tf32(acc[mb], a0, a1, a2, a3, b.x, b.y);
+            }
+        }
+        __syncwarp();
+    }
+
+    // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
+    const size_t ldc = (size_t)ldb;
+    float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
+    if constexpr (CLS == 1)
+    {
+        const int r = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < NS / 8; nb++)
+        {
+            float *p0 = cbase + (size_t)r * ldc + nb * 8 + c, *p1 = p0 + 8 * ldc;
+            if (split)
+            {
+                atomicAdd(p0, acc[nb][0]); atomicAdd(p0 + 1, acc[nb][1]);
+                atomicAdd(p1, acc[nb][2]); atomicAdd(p1 + 1, acc[nb][3]);
+            }
+            else
+            {
+                *reinterpret_cast<float2 *>(p0) = make_float2(acc[nb][0], acc[nb][1]);
+                *reinterpret_cast<float2 *>(p1) = make_float2(acc[nb][2], acc[nb][3]);
+            }
+        }
+    }
+    else
+    {
+        // the MMA computed the transposed block: accumulator (m, n) is C[row n][column m]
+        const int m = lane >> 2, n = (lane & 3) * 2;
+#pragma unroll
+        for (int mb = 0; mb < NS / 16; mb++)
+        {
+            float *p = cbase + (size_t)n * ldc + mb * 16 + m;
+            if (split)
+            {
+                atomicAdd(p, acc[mb][0]); atomicAdd(p + ldc, acc[mb][1]);
+                atomicAdd(p + 8, acc[mb][2]); atomicAdd(p + ldc + 8, acc[mb][3]);
+            }
+            else
+            {
+                p[0] = acc[mb][0]; p[ldc] = acc[mb][1];
+                p[8] = acc[mb][2]; p[ldc + 8] = acc[mb][3];
+            }
+        }
+    }
+}
+
+template <int PREC, int CLS, int NS>
+int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)
+{
+    using Cfg = SmallCfg<PREC, CLS, NS>;
+    TspClass &c = h->cls[CLS];
+    static bool configured[8] = {false};
+    auto kern = k_spmm_small<PREC, CLS, NS>;
+    if (!configured[h->device & 7])
+    {
+        TSP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        configured[h->device & 7] = true;
+    }
+    const int nstripes = colB / NS;
+    const long long units = (long long)c.ntasks * nstripes;
+    const int grid = (int)((units + WARPS - 1) / WARPS);
+    if (grid == 0) return TSP_OK;
+    kern<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_row, c.d_task_start, c.d_tile_colidx,
+                                            (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c);
+    TSP_CUDA(cudaGetLastError());
+    h->launches++;
+    return TSP_OK;
+}
+
+template <int PREC, int CLS>
+int launch_width(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)
+{
+    if (colB == 32) return launch_one<PREC, CLS, 32>(h, d_b, d_c, colB, s);
+    if (colB % 128 == 0) return launch_one<PREC, CLS, 128>(h, d_b, d_c, colB, s);
+    return launch_one<PREC, CLS, 64>(h, d_b, d_c, colB, s);
+}
+
+template <int PREC, int CLS, int NS>
+void resources_one(TspKernelResources *out)
+{
+    using Cfg = SmallCfg<PREC, CLS, NS>;
+    cudaFuncAttributes attr;
+    memset(&attr, 0, sizeof(attr));
+    cudaFuncGetAttributes(&attr, k_spmm_small<PREC, CLS, NS>);
+    out->threads = WARPS * 32;
+    out->registers_per_thread = attr.numRegs;
+    out->shared_bytes = Cfg::SMEM + (long long)attr.sharedSizeBytes;
+    out->tasks_per_block = WARPS;
+    out->iteration_bytes = WARPS * Cfg::STAGE_BYTES;
+}
+
+}  // namespace
+
+// Zeroes the C rows of split panels (their tasks accumulate with atomics).  Upstream clears all of C
+// with cudaMemset outside its timers (src/csr2tile.h:1024, 1038).
+__global__ void k_clear_split_rows(int nsplit, const int *__restrict__ split_row, int bm, int row_begin, int ldc, float *__restrict__ dC)
+{
+    const int p = blockIdx.x;
+    if (p >= nsplit) return;
+    float4 *dst = reinterpret_cast<float4 *>(dC + (size_t)(split_row[p] - row_begin) * ldc);
+    const int n4 = bm * ldc / 4;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s)
+{
+    for (int k = 0; k < 3; k++)
+    {
+        TspClass &c = h->cls[k];
+        if (c.tilenum == 0 || c.nsplit == 0) continue;
+        k_clear_split_rows<<<c.nsplit, 256, 0, s>>>(c.nsplit, c.d_split_row, c.BM, h->row_begin, colB, d_c);
+        TSP_CUDA(cudaGetLastError());
+        h->launches++;
+    }
+    return TSP_OK;
+}
+
+int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s)
+{
+    if (h->precision == 0)
+        return cls == 1 ? launch_width<0, 1>(h, d_b, d_c, colB, s) : launch_width<0, 2>(h, d_b, d_c, colB, s);
+    return cls == 1 ? launch_width<1, 1>(h, d_b, d_c, colB, s) : launch_width<1, 2>(h, d_b, d_c, colB, s);
+}
+
+void tsp_small_resources(int precision, int cls, int colB, TspKernelResources *out)
+{
+    const int ns = colB == 32 ? 32 : (colB % 128 == 0 ? 128 : 64);
+#define TSP_RES(P, C)                                                  \
+    do {                                                               \
+        if (ns == 32) resources_one<P, C, 32>(out);                    \
+        else if (ns == 64) resources_one<P, C, 64>(out);               \
+        else resources_one<P, C, 128>(out);                            \
+    } while (0)
+    if (precision == 0) { if (cls == 1) TSP_RES(0, 1); else TSP_RES(0, 2); }
+    else { if (cls == 1) TSP_RES(1, 1); else TSP_RES(1, 2); }
+#undef TSP_RES
+}

@@ -1,0 +1,134 @@
+// Internal declarations shared by the translation units of libtilespmm_b200.so.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include <vector>
+
+#include "../../include/tilespmm_b200.h"
+
+// ---------------------------------------------------------------- errors
+
+void tsp_set_error(const char *fmt, ...);
+
+#define TSP_CUDA(call)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (call);                                                                   \
+        if (e__ != cudaSuccess) {                                                                   \
+            tsp_set_error("%s:%d %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString(e__));    \
+            return e__ == cudaErrorMemoryAllocation ? TSP_ENOMEM : TSP_ECUDA;                       \
+        }                                                                                           \
+    } while (0)
+
+#define TSP_TRY(call)                  \
+    do {                               \
+        int rc__ = (call);             \
+        if (rc__ != TSP_OK) return rc__; \
+    } while (0)
+
+// ---------------------------------------------------------------- tile geometry and layouts
+
+__host__ __device__ inline int tsp_bm(int cls) { return cls == 0 ? 64 : (cls == 1 ? 16 : 8); }
+__host__ __device__ inline int tsp_bn(int precision, int cls)
+{
+    return precision == 0 ? (cls == 0 ? 32 : 16) : (cls == 0 ? 16 : 8);
+}
+
+// Position of element (r, c) of a 16 x KW block in mma.sync A-fragment order (KW = 16 FP16 / 8 TF32):
+// lane l = (r%8)*4 + ..., each lane owns 8 halves / 4 floats.  This is the order upstream stores 16-row
+// tiles in (src/csr2tile.h:289-307) and the order one 16-byte load per lane wants.
+__host__ __device__ inline int tsp_frag16_index(int precision, int r, int c)
+{
+    if (precision == 0) return ((((r & 7) << 2) + ((c & 7) >> 1)) << 3) + ((c >> 3) << 2) + ((r >> 3) << 1) + (c & 1);
+    return ((((r & 7) << 2) + (c & 3)) << 2) + ((c >> 2) << 1) + (r >> 3);
+}
+
+// Position of (r, c) inside one tile in the upstream layout (src/csr2tile.h:255-373).
+__host__ __device__ inline int tsp_upstream_index(int precision, int cls, int r, int c)
+{
+    if (cls == 2)  // 8-row tile = the k x n8 operand of the MMA (src/csr2tile.h:262-271)
+    {
+        if (precision == 0) return (((r << 2) + ((c >> 1) & 3)) << 2) + ((c >> 3) << 1) + (c & 1);
+        return (((r << 2) + (c & 3)) << 1) + (c >> 2);
+    }
+    if (cls == 1) return tsp_frag16_index(precision, r, c);
+    const int KW = precision == 0 ? 16 : 8;  // 64-row: 4 x 2 sub-blocks, sub_m-major (src/csr2tile.h:319-372)
+    return ((r >> 4) * 2 + c / KW) * 16 * KW + tsp_frag16_index(precision, r & 15, c % KW);
+}
+
+// Position (in elements) of (r, k) inside one 64-row tile as the DEVICE keeps it: the K-major, no-swizzle
+// shared-memory operand layout of tcgen05.mma.  A core matrix is 8 rows x 16 bytes (T = 8 halves / 4 floats),
+// stored as 128 contiguous bytes; core matrix (mi = r/8, ki = k/T) sits at byte (ki*8 + mi)*128, so that one
+// K-slice of an MMA (two core-matrix columns, 2 KB) is contiguous and a whole tile is one 4 KB bulk copy.
+__host__ __device__ inline int tsp_umma_index(int precision, int r, int k)
+{
+    const int T = precision == 0 ? 8 : 4;
+    return ((k / T) * 8 + (r >> 3)) * 8 * T + (r & 7) * T + (k % T);
+}
+
+// Position of (r, c) in the layout the device stores for class cls.
+__host__ __device__ inline int tsp_device_index(int precision, int cls, int r, int c)
+{
+    return cls == 0 ? tsp_umma_index(precision, r, c) : tsp_upstream_index(precision, cls, r, c);
+}
+
+// ---------------------------------------------------------------- handle
+
+struct TspKernelResources  // what the platform probe records per (class, width) kernel
+{
+    int threads, registers_per_thread, iteration_bytes, tasks_per_block;
+    long long shared_bytes;
+};
+
+struct TspClass
+{
+    int BM = 0, BN = 0;
+    int rows = 0;            // rows of the shard assigned to this class
+    long long nnz = 0;
+    int tilem = 0, tilenum = 0;
+    int *d_tile_ptr = nullptr, *d_tile_nnz = nullptr, *d_tile_colidx = nullptr, *d_panel_row = nullptr;
+    void *d_val = nullptr;
+    std::vector<int> h_tile_ptr, h_panel_row;
+    // schedule for the current threshold
+    int TH = 0, ntasks = 0, nsplit = 0;
+    long long cap_tasks = 0;
+    unsigned int *d_task_row = nullptr;
+    int *d_task_start = nullptr, *d_split_row = nullptr, *d_task_count = nullptr;
+};
+
+struct tsp_handle
+{
+    int device = 0, precision = 0;
+    cudaDeviceProp prop;
+    int rowA = 0, colA = 0;
+    long long nnzA = 0;
+    bool converted = false;
+    int row_begin = 0, row_end = 0;   // C slab of this shard (original rows)
+    TspClass cls[3];
+    cudaStream_t side[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+    long long launches = 0;
+    int *d_error = nullptr;           // device-side error flag (bounded waits)
+    void *stage_b = nullptr;          // device staging of the host-buffer entry points
+    float *stage_c = nullptr;
+    size_t stage_b_bytes = 0, stage_c_bytes = 0;
+};
+
+// ---------------------------------------------------------------- cross-TU entry points
+
+int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz, const int *d_rowptr, const int *d_colidx,
+                     const void *d_val, float gamma, float delta, int shard_index, int shard_count);
+void tsp_free_tiles(tsp_handle *h);
+int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst);
+
+// class kernels; C is addressed relative to row_begin.  count_only != 0 skips the launch and only reports
+// how many launches the call would make.
+int tsp_launch_class64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s);
+int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
+int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
+void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);
+int tsp_spmm64_init(tsp_handle *h);
