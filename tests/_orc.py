@@ -18,6 +18,8 @@ def BN(precision, cls):
 
 def to_values(vals_f32, precision):
     """FP16 bit patterns (uint16) for precision 0, float32 for precision 1 (TF32 inputs are plain floats)."""
+    if isinstance(vals_f32, np.ndarray) and vals_f32.dtype == np.uint16:
+        return np.ascontiguousarray(vals_f32)          # already FP16 bit patterns
     vals_f32 = np.ascontiguousarray(vals_f32, dtype=np.float32)
     if precision == 0:
         return vals_f32.astype(np.float16).view(np.uint16)
@@ -135,7 +137,7 @@ def spmm_csr(precision, shape, rowptr, colidx, vals, B, ncols, trunc=True):
     L = Orc.lib()
     rowptr = np.ascontiguousarray(rowptr, np.int32)
     colidx = np.ascontiguousarray(colidx, np.int32)
-    v = to_values(vals, precision) if vals.dtype != np.uint16 else vals
+    v = to_values(vals, precision)
     B = np.ascontiguousarray(B)
     Cm = np.zeros((shape[0], ncols), dtype=np.float32)
     L.orc_spmm_csr(precision, int(trunc), 0, shape[0], _ptr(rowptr), _ptr(colidx), _ptr(v), _ptr(B), B.shape[1], ncols,

@@ -44,6 +44,11 @@ def test_tiling_bit_exact_vs_upstream_golden(name, prec):
         for cls in range(3):
             for TH in (8, 24, 64):
                 rows, cs = m.schedule(cls, TH)
+                if rec["info"][cls][3] == 0:
+                    # upstream builds no schedule for a class without tiles (src/csr2tile.h:662) and relies on a
+                    # cleared C; here such a class gets one empty task per panel, which writes the zeros
+                    assert rows.size == rec["info"][cls][2] and not cs.any() and not (rows >> 31).any()
+                    continue
                 assert [int(rows.size), h(rows), h(cs)] == rec["sched"][f"{cls}:{TH}"], (name, prec, g, d, cls, TH)
     m.close()
 

@@ -172,7 +172,7 @@ class TileMatrix:
         n = C.c_int(0)
         _check(self.L.tsp_export_schedule(self.h, cls, C.byref(n), None, None), "tsp_export_schedule")
         rows = np.zeros(n.value, dtype=np.uint32)
-        colstart = np.zeros(n.value + 1 if n.value else 0, dtype=np.int32)
+        colstart = np.zeros(n.value + 1, dtype=np.int32)
         if n.value:
             _check(self.L.tsp_export_schedule(self.h, cls, C.byref(n), _p(rows), _p(colstart)), "tsp_export_schedule")
         return rows, colstart

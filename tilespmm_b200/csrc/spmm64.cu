@@ -5,7 +5,7 @@
 // column stripe of up to 256 columns, so the A tiles and column indices are read once per 256 columns
 // (upstream: once per 64).  Roles:
 //   warps 0-3  producers: gather the B rows named by tile_colidx with 16-byte cp.async into a STAGES-deep ring,
-//              writing the 128-byte-swizzled MN-major operand layout tcgen05.mma reads, plus the A tile, which
+//              writing the swizzled MN-major operand layout tcgen05.mma reads, plus the A tile, which
 //              the conversion already stores in the K-major core-matrix order (a straight 4 KB copy);
 //              afterwards they are the epilogue: tcgen05.ld of the 64 x N FP32 accumulator -> C.
 //   warp 4     allocates tensor memory; one elected lane issues two tcgen05.mma (M=64, N=stripe, K=16 FP16 /
@@ -34,10 +34,16 @@ struct Cfg64
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = N >= 128 ? 4 : (N == 64 ? 6 : 8);
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;  // + slack to align the ring to 1 KB
-    static constexpr bool SW128 = RB >= 128;
-    static constexpr int ATOM_BYTES = SW128 ? 1024 : 512;     // 8 K-rows x 128 B (or 64 B)
-    static constexpr int KATOMS = BNK / 8;                    // atoms along K per tile
-    static constexpr int KATOMS_PER_MMA = PREC == 0 ? 2 : 1;  // K = 16 halves / 8 floats per instruction
+    // Shared-memory layout of the gathered rows (the MN-major B operand):
+    //   FP16, rows >= 128 B : 128-byte swizzle, atoms of 8 K-rows x 128 B, 16-byte chunks XORed with the row
+    //   FP16, 64-byte rows  : 64-byte swizzle, atoms of 8 K-rows x 64 B
+    //   TF32                : the only MN-major mode for 32-bit operands, "128-byte swizzle with 32-byte
+    //                         atomicity": atoms of 4 K-rows x 128 B, 32-byte chunks XORed with the row
+    static constexpr int MODE = PREC == 1 ? 1 : (RB >= 128 ? 2 : 4);   // layout-type field of the descriptor
+    static constexpr int ATOM_ROWS = PREC == 1 ? 4 : 8;
+    static constexpr int ATOM_BYTES = ATOM_ROWS * (RB >= 128 ? 128 : 64);
+    static constexpr int KATOMS = BNK / ATOM_ROWS;            // atoms along K per tile (4)
+    static constexpr int KATOMS_PER_MMA = 2;                  // K = 16 halves = 2x8 rows / 8 floats = 2x4 rows
     static constexpr int TMEM_COLS = N < 32 ? 32 : N;
     static constexpr int B_ITERS = (BNK * CPR) / (PRODUCER_WARPS * 32);
 };
@@ -161,9 +167,10 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
 #pragma unroll
         for (int it = 0; it < C::B_ITERS; it++)
         {
-            const int q = it * (PRODUCER_WARPS * 32) + tid, k = q / C::CPR, c = q % C::CPR, ka = k >> 3, kr = k & 7;
-            if (C::SW128) dst_off[it] = ((c >> 3) * C::KATOMS + ka) * 1024 + kr * 128 + (((c & 7) ^ kr) << 4);
-            else dst_off[it] = ka * 512 + kr * 64 + ((c ^ ((kr >> 1) & 3)) << 4);
+            const int q = it * (PRODUCER_WARPS * 32) + tid, k = q / C::CPR, c = q % C::CPR;
+            if (C::MODE == 2) { const int ka = k >> 3, kr = k & 7; dst_off[it] = ((c >> 3) * C::KATOMS + ka) * 1024 + kr * 128 + (((c & 7) ^ kr) << 4); }
+            else if (C::MODE == 4) { const int ka = k >> 3, kr = k & 7; dst_off[it] = ka * 512 + kr * 64 + ((c ^ ((kr >> 1) & 3)) << 4); }
+            else { const int ka = k >> 2, kr = k & 3; dst_off[it] = ((c >> 3) * C::KATOMS + ka) * 512 + kr * 128 + (((((c & 7) >> 1) ^ kr) << 5) | ((c & 1) << 4)); }
             cols_next[it] = nt > 0 ? __ldg(tile_colidx + (size_t)t0 * C::BNK + k) : 0;
         }
         auto publish = [&](int i) {  // tile i is complete in shared memory: hand it to the MMA warp
@@ -263,7 +270,7 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
                 const unsigned long long da = make_desc(st + kk * 2048, 1024, 128, 0);
                 // B: MN-major; 64-column (128-byte) atoms KATOMS KB apart, K atoms ATOM_BYTES apart
                 const unsigned long long db = make_desc(st + C::A_BYTES + kk * C::KATOMS_PER_MMA * C::ATOM_BYTES,
-                                                        C::KATOMS * C::ATOM_BYTES, C::ATOM_BYTES, C::SW128 ? 2u : 4u);
+                                                        C::KATOMS * C::ATOM_BYTES, C::ATOM_BYTES, (unsigned)C::MODE);
                 umma<PREC>(tmem_base, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(bar_empty + 8 * s);  // frees the slot when these MMAs have read it
