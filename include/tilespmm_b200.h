@@ -83,6 +83,19 @@ int tsp_kernel_info(const tsp_handle *h, int cls, int colB_padded, long long *ou
 /* upstream tile_pretreatment + update_metadata (src/csr2tile.h:383-434, 644-711): builds the task arrays of
  * class cls for threshold TH on the device. */
 int tsp_schedule(tsp_handle *h, int cls, int TH);
+/* No counterpart in upstream.  The same task arrays as tsp_schedule(), built without cudaMalloc/cudaFree or
+ * any allocating library call, for hosts that own all device memory themselves (a pre-carved arena) or may
+ * not enter the allocator on their hot path.  The per-panel counters live in a fixed device array inside
+ * the library (4 MB per GPU, held until the process exits), so tilem is limited to 1,048,576 panels
+ * (TSP_EINVAL beyond that).  Inputs d_tile_ptr[tilem+1], d_panel_row[tilem]; outputs d_task_row[capacity],
+ * d_task_start[capacity+1], d_split_row[tilem] (may be NULL) are caller-owned device arrays; *ntasks and
+ * *nsplit are host outputs.  TSP_ENOMEM (with *ntasks = tasks needed, nothing written) when capacity is too
+ * small.  The first call on a device resolves the array's device address: make it before any stream capture.
+ * Calls share the array: back-to-back calls are fine, calls that can overlap on one GPU race.  Waits for
+ * `stream` before returning. */
+int tsp_schedule_noalloc(int device, int tilem, int TH, const int *d_tile_ptr, const int *d_panel_row,
+                         unsigned int *d_task_row, int *d_task_start, long long capacity, int *d_split_row,
+                         int *ntasks, int *nsplit, void *stream);
 /* Current task arrays: rows[ntasks] (bit 31 = slice of a split panel), colstart[ntasks+1]; NULL = count only. */
 int tsp_export_schedule(const tsp_handle *h, int cls, int *ntasks, unsigned int *h_rows, int *h_colstart);
 /* On-GPU threshold tuning, upstream src/csr2tile.h:964-1019: every combination of the candidate thresholds,

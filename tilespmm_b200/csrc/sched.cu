@@ -209,3 +209,154 @@ int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
     for (int i = 0; i < 4; i++) top4[i] = i < ncand ? cand_th[i] : cand_th[0];
     return TSP_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Scheduling without any allocation.
+//
+// tsp_schedule() above sizes and allocates its per-panel counters and its scan workspace with cudaMalloc.
+// Some hosts cannot do that at the point where they need a new schedule: a solver or serving process that
+// carves all device memory into its own arena at start-up (so a later cudaMalloc may simply fail, and
+// cudaMalloc/cudaFree would stall the whole device on its hot path), or a real-time loop that is not allowed
+// to enter the allocator at all.  For them tsp_schedule_noalloc() does the same work with the per-panel
+// counters kept in the fixed device array below, which every GPU that loads this library holds until the
+// process exits (4 MB + 256 B).  The caller provides the tile pointers, the panel rows and the output arrays.
+// ---------------------------------------------------------------------------------------------------------
+
+#define TSP_NOALLOC_MAX_PANELS (1 << 20)
+
+// [0 .. tilem]            per-panel task counts, scanned in place
+// [MAX_PANELS + 1 ...]    counter of split panels
+static __device__ __align__(256) int g_noalloc_scratch[TSP_NOALLOC_MAX_PANELS + 1 + 64];
+
+namespace
+{
+
+// In-place exclusive scan of a[0..n) by ONE block (n <= about a million ints: a few passes of 1024 threads).
+__global__ void k_scan_one_block(int *a, int n)
+{
+    __shared__ int warp_sum[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < n; base += blockDim.x)
+    {
+        const int i = base + threadIdx.x;
+        const int v = i < n ? a[i] : 0;
+        int x = v;
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        if (lane == 31) warp_sum[warp] = x;
+        __syncthreads();
+        if (warp == 0)
+        {
+            int w = warp_sum[lane];
+            for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += y; }
+            warp_sum[lane] = w;
+        }
+        __syncthreads();
+        const int before = carry + (warp ? warp_sum[warp - 1] : 0) + x - v;
+        if (i < n) a[i] = before;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + v;
+        __syncthreads();
+    }
+}
+
+// Same output as k_task_fill, but never writes past the caller's capacity.
+__global__ void k_task_fill_bounded(int tilem, const int *__restrict__ tile_ptr, const int *__restrict__ panel_row, int TH,
+                                    const int *__restrict__ task_base, long long capacity, unsigned int *__restrict__ task_row,
+                                    int *__restrict__ task_start, int *__restrict__ split_row, int *__restrict__ split_count)
+{
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= tilem) return;
+    if (task_base[tilem] > capacity) return;  // the host reports the overflow; nothing is written
+    const int t0 = tile_ptr[p], len = tile_ptr[p + 1] - t0, b = task_base[p], row = panel_row[p];
+    if (p == 0) task_start[0] = t0;
+    if (len <= TH)
+    {
+        task_row[b] = (unsigned int)row;
+        task_start[b + 1] = t0 + len;
+        return;
+    }
+    const int parts = (len + TH - 1) / TH, each = (len + parts - 1) / parts;
+    for (int s = 0; s < parts; s++)
+    {
+        task_row[b + s] = (unsigned int)row | 0x80000000u;
+        task_start[b + s + 1] = s == parts - 1 ? t0 + len : t0 + (s + 1) * each;
+    }
+    const int slot = atomicAdd(split_count, 1);
+    if (split_row) split_row[slot] = row;
+}
+
+int *g_noalloc_ptr[64];       // device address of g_noalloc_scratch per device, resolved on first use
+bool g_noalloc_ready[64];
+
+}  // namespace
+
+// Builds the task arrays of one tile class for threshold TH -- the same arrays tsp_schedule() builds -- without
+// calling cudaMalloc, cudaFree or any allocating library routine.
+//
+//   d_tile_ptr[tilem+1], d_panel_row[tilem]   inputs (device): tiles per panel (prefix sums) and first rows
+//   d_task_row[capacity], d_task_start[capacity+1]   outputs (device), caller-allocated
+//   d_split_row[tilem]                        output (device, may be NULL): first rows of the split panels
+//   *ntasks, *nsplit                          outputs (host)
+//
+// Limits and rules:
+//   * tilem <= TSP_NOALLOC_MAX_PANELS (1,048,576 panels); more is refused with TSP_EINVAL.  If the schedule
+//     needs more than `capacity` tasks the call returns TSP_ENOMEM, *ntasks holds the number needed and the
+//     output arrays are left untouched.
+//   * The first call on a device looks up the device address of the scratch array (with that device current);
+//     make that first call before starting a stream capture.
+//   * All calls share the one scratch array per device.  Each call clears what it needs at its start, so calls
+//     one after another on the same stream are fine; two calls whose kernels can overlap on the GPU (different
+//     streams or threads, same device) race on it and must be serialised by the caller.
+//   * The call waits for `stream` before it returns (it has to read the task count back).
+extern "C" int tsp_schedule_noalloc(int device, int tilem, int TH, const int *d_tile_ptr, const int *d_panel_row,
+                                    unsigned int *d_task_row, int *d_task_start, long long capacity, int *d_split_row,
+                                    int *ntasks, int *nsplit, void *stream)
+{
+    if (tilem < 0 || TH <= 0 || !d_tile_ptr || !d_panel_row || !d_task_row || !d_task_start || capacity < 0 || !ntasks || device < 0 || device >= 64)
+    {
+        tsp_set_error("schedule_noalloc: bad argument");
+        return TSP_EINVAL;
+    }
+    if (tilem > TSP_NOALLOC_MAX_PANELS)
+    {
+        tsp_set_error("schedule_noalloc: %d panels exceed the fixed scratch of %d panels; use tsp_schedule()", tilem, TSP_NOALLOC_MAX_PANELS);
+        return TSP_EINVAL;
+    }
+    TSP_CUDA(cudaSetDevice(device));
+    if (!g_noalloc_ready[device])
+    {
+        // In host code the array's name is only a handle for the runtime, not a device address.
+        void *p = nullptr;
+        TSP_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_ptr[device] = (int *)p;
+        g_noalloc_ready[device] = true;
+    }
+    int *counts = g_noalloc_ptr[device];
+    int *split_count = counts + TSP_NOALLOC_MAX_PANELS + 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    *ntasks = 0;
+    if (nsplit) *nsplit = 0;
+    if (tilem == 0) return TSP_OK;
+    const int T = 256;
+    TSP_CUDA(cudaMemsetAsync(split_count, 0, sizeof(int), s));  // the array keeps the previous call's contents
+    k_task_counts<<<(tilem + 1 + T - 1) / T, T, 0, s>>>(tilem, d_tile_ptr, TH, counts);
+    k_scan_one_block<<<1, 1024, 0, s>>>(counts, tilem + 1);
+    k_task_fill_bounded<<<(tilem + T - 1) / T, T, 0, s>>>(tilem, d_tile_ptr, d_panel_row, TH, counts, capacity, d_task_row, d_task_start,
+                                                         d_split_row, split_count);
+    TSP_CUDA(cudaGetLastError());
+    int total = 0, splits = 0;
+    TSP_CUDA(cudaMemcpyAsync(&total, counts + tilem, sizeof(int), cudaMemcpyDeviceToHost, s));
+    TSP_CUDA(cudaMemcpyAsync(&splits, split_count, sizeof(int), cudaMemcpyDeviceToHost, s));
+    TSP_CUDA(cudaStreamSynchronize(s));
+    *ntasks = total;
+    if ((long long)total > capacity)
+    {
+        tsp_set_error("schedule_noalloc: the schedule needs %d tasks but the output arrays hold %lld", total, capacity);
+        return TSP_ENOMEM;
+    }
+    if (nsplit) *nsplit = splits;
+    return TSP_OK;
+}
