@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cusparse", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--th", default=None, help="th64,th16,th8: fixed thresholds, skips the on-GPU tuning (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -252,7 +253,13 @@ def main():
     dC = torch.empty((m.c_rows(), cb), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
 
-    best_th, tune_ms = m.tune(dB, dC, cb)
+    if args.th:
+        best_th, tune_ms = [int(x) for x in args.th.split(",")], 0.0
+        for cls in range(3):
+            if info[cls, 2] > 0:
+                m.schedule(cls, best_th[cls])
+    else:
+        best_th, tune_ms = m.tune(dB, dC, cb)
 
     def barrier():
         if world > 1:

@@ -12,7 +12,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtilespmm_b200.so")
+LIB_PATH = os.environ.get("TILESPMM_B200_LIB") or os.path.join(HERE, "libtilespmm_b200.so")
 CLASSES = (64, 16, 8)
 ARRAYS = ("orig_row", "tile_ptr", "tile_nnz", "tile_colidx", "tile_val", "panel_row")
 _lib = None

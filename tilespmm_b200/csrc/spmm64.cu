@@ -18,13 +18,13 @@
 namespace
 {
 
-constexpr int PRODUCER_WARPS = 4;
-constexpr int THREADS64 = (PRODUCER_WARPS + 1) * 32;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 template <int PREC, int N>
 struct Cfg64
 {
+    static constexpr int PW = N >= 128 ? 8 : 4;               // producer (and epilogue) warps
+    static constexpr int THREADS = (PW + 1) * 32;
     static constexpr int SZ = PREC == 0 ? 2 : 4;
     static constexpr int BNK = PREC == 0 ? 32 : 16;           // K extent of a tile
     static constexpr int A_BYTES = 64 * BNK * SZ;             // 4096
@@ -32,7 +32,10 @@ struct Cfg64
     static constexpr int CPR = RB / 16;
     static constexpr int B_BYTES = BNK * RB;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    // ring depth and how many tiles the producers run ahead of what they have published: a slot is reused
+    // STAGES tiles later, LAG+1 tiles are in flight to memory, and the MMA has STAGES-LAG tiles of slack
     static constexpr int STAGES = N >= 128 ? 4 : (N == 64 ? 6 : 8);
+    static constexpr int LAG = N >= 128 ? 2 : 4;
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;  // + slack to align the ring to 1 KB
     // Shared-memory layout of the gathered rows (the MN-major B operand):
     //   FP16, rows >= 128 B : 128-byte swizzle, atoms of 8 K-rows x 128 B, 16-byte chunks XORed with the row
@@ -45,7 +48,9 @@ struct Cfg64
     static constexpr int KATOMS = BNK / ATOM_ROWS;            // atoms along K per tile (4)
     static constexpr int KATOMS_PER_MMA = 2;                  // K = 16 halves = 2x8 rows / 8 floats = 2x4 rows
     static constexpr int TMEM_COLS = N < 32 ? 32 : N;
-    static constexpr int B_ITERS = (BNK * CPR) / (PRODUCER_WARPS * 32);
+    static constexpr int B_ITERS = (BNK * CPR) / (PW * 32);
+    static constexpr int A_ITERS = A_BYTES / 16 / (PW * 32);
+    static constexpr int KPI = PW * 32 / CPR;                 // tile rows covered by one CTA-wide copy
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -119,13 +124,13 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32])
 }
 
 template <int PREC, int N>
-__global__ void __launch_bounds__(THREADS64)
+__global__ void __launch_bounds__(Cfg64<PREC, N>::THREADS)
 k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ task_row, const int *__restrict__ task_start,
          const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val, const unsigned char *__restrict__ dB,
          float *__restrict__ dC, int *__restrict__ err)
 {
     using C = Cfg64<PREC, N>;
-    constexpr int S = C::STAGES;
+    constexpr int S = C::STAGES, PRODUCER_WARPS = C::PW;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * C::STAGES + 1];
     __shared__ unsigned tmem_slot;
@@ -160,18 +165,24 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
     if (warp < PRODUCER_WARPS)
     {
         // ------------------------------------------------------------ producers
-        const size_t ldb_bytes = (size_t)ldb * C::SZ, stripe_bytes = (size_t)stripe * C::RB;
+        // Chunk q = it*PW*32 + tid of a tile is 16-byte chunk c = tid % CPR of row k = it*KPI + tid/CPR, so the
+        // source column offset and the swizzled destination of every copy are loop invariants.
+        const unsigned ldb_b = (unsigned)ldb * C::SZ;
+        const int c_mine = tid % C::CPR, k_mine = tid / C::CPR;
+        const unsigned char *gsrc = dB + (size_t)stripe * C::RB + (size_t)c_mine * 16;
+        const int *idx_ptr = tile_colidx + (size_t)t0 * C::BNK + k_mine;
+        const unsigned char *a_src = tile_val + (size_t)t0 * C::A_BYTES + tid * 16;
         int cols_next[C::B_ITERS];
-        // chunk q = it*128 + tid of a tile: row k = q / CPR, 16-byte chunk c = q % CPR
         unsigned dst_off[C::B_ITERS];
 #pragma unroll
         for (int it = 0; it < C::B_ITERS; it++)
         {
-            const int q = it * (PRODUCER_WARPS * 32) + tid, k = q / C::CPR, c = q % C::CPR;
+            const int k = it * C::KPI + k_mine, c = c_mine;
             if (C::MODE == 2) { const int ka = k >> 3, kr = k & 7; dst_off[it] = ((c >> 3) * C::KATOMS + ka) * 1024 + kr * 128 + (((c & 7) ^ kr) << 4); }
             else if (C::MODE == 4) { const int ka = k >> 3, kr = k & 7; dst_off[it] = ka * 512 + kr * 64 + ((c ^ ((kr >> 1) & 3)) << 4); }
             else { const int ka = k >> 2, kr = k & 3; dst_off[it] = ((c >> 3) * C::KATOMS + ka) * 512 + kr * 128 + (((((c & 7) >> 1) ^ kr) << 5) | ((c & 1) << 4)); }
-            cols_next[it] = nt > 0 ? __ldg(tile_colidx + (size_t)t0 * C::BNK + k) : 0;
+            dst_off[it] += C::A_BYTES;
+            cols_next[it] = nt > 0 ? __ldg(idx_ptr + it * C::KPI) : 0;
         }
         auto publish = [&](int i) {  // tile i is complete in shared memory: hand it to the MMA warp
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -185,28 +196,24 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
             if (i >= S) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1));  // warp-uniform outcome
             if (!ok) break;
             const unsigned st = ring + s * C::STAGE_BYTES;
-            const unsigned char *a_src = tile_val + (size_t)(t0 + i) * C::A_BYTES;
 #pragma unroll
-            for (int q = 0; q < C::A_BYTES / 16 / (PRODUCER_WARPS * 32); q++)
-                cp_async16(st + (q * (PRODUCER_WARPS * 32) + tid) * 16, a_src + (q * (PRODUCER_WARPS * 32) + tid) * 16);
+            for (int q = 0; q < C::A_ITERS; q++) cp_async16(st + (q * (PRODUCER_WARPS * 32) + tid) * 16, a_src + q * (PRODUCER_WARPS * 32) * 16);
+            a_src += C::A_BYTES;
 #pragma unroll
             for (int it = 0; it < C::B_ITERS; it++)
-            {
-                const int c = (it * (PRODUCER_WARPS * 32) + tid) % C::CPR;
-                cp_async16(st + C::A_BYTES + dst_off[it], dB + (size_t)cols_next[it] * ldb_bytes + stripe_bytes + c * 16);
-            }
+                cp_async16(st + dst_off[it], gsrc + (unsigned long long)(unsigned)cols_next[it] * ldb_b);
             cp_async_commit();
+            idx_ptr += C::BNK;
             if (i + 1 < nt)
             {
 #pragma unroll
-                for (int it = 0; it < C::B_ITERS; it++)
-                    cols_next[it] = __ldg(tile_colidx + (size_t)(t0 + i + 1) * C::BNK + (it * (PRODUCER_WARPS * 32) + tid) / C::CPR);
+                for (int it = 0; it < C::B_ITERS; it++) cols_next[it] = __ldg(idx_ptr + it * C::KPI);
             }
-            if (i >= S - 1)
+            if (i >= C::LAG)
             {
-                cp_async_wait<S - 1>();  // the group of tile i-(S-1) has landed
-                publish(i - (S - 1));
-                published = i - (S - 1) + 1;
+                cp_async_wait<C::LAG>();  // the group of tile i-LAG has landed
+                publish(i - C::LAG);
+                published = i - C::LAG + 1;
             }
         }
         cp_async_wait<0>();
@@ -222,13 +229,17 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
         if (ok)
         {
             // with M = 64 the accumulator row r lives in tensor-memory lane (r/16)*32 + r%16
-            const int row = warp * 16 + (lane & 15);
+            // a warp reads the 32 lanes of its quarter (warp % 4); with 8 epilogue warps each quarter is shared
+            // by two warps that take one half of the columns each
+            const int quarter = warp & 3, part = warp >> 2;
+            constexpr int COLS_PER_WARP = N / (PRODUCER_WARPS / 4);
+            const int row = quarter * 16 + (lane & 15);
             float *crow = dC + (size_t)(first_row + row) * (size_t)ldb + (size_t)stripe * N;
 #pragma unroll 1
-            for (int c0 = 0; c0 < N; c0 += 32)
+            for (int c0 = part * COLS_PER_WARP; c0 < (part + 1) * COLS_PER_WARP; c0 += 32)
             {
                 unsigned r[32];
-                if (nt > 0) tmem_ld32(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0, r);
+                if (nt > 0) tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
                 else
                 {
 #pragma unroll
@@ -301,7 +312,7 @@ int launch64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t 
     }
     if (c.ntasks == 0) return TSP_OK;
     dim3 grid(c.ntasks, colB / N);
-    kern<<<grid, THREADS64, C::SMEM, s>>>(c.ntasks, colB, h->row_begin, c.d_task_row, c.d_task_start, c.d_tile_colidx,
+    kern<<<grid, C::THREADS, C::SMEM, s>>>(c.ntasks, colB, h->row_begin, c.d_task_row, c.d_task_start, c.d_tile_colidx,
                                          (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error);
     TSP_CUDA(cudaGetLastError());
     h->launches++;
@@ -324,7 +335,7 @@ void resources64(TspKernelResources *out)
     cudaFuncAttributes attr;
     memset(&attr, 0, sizeof(attr));
     cudaFuncGetAttributes(&attr, k_spmm64<PREC, N>);
-    out->threads = THREADS64;
+    out->threads = C::THREADS;
     out->registers_per_thread = attr.numRegs;
     out->shared_bytes = C::SMEM + (long long)attr.sharedSizeBytes;
     out->tasks_per_block = 1;

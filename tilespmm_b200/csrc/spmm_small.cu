@@ -16,13 +16,26 @@
 namespace
 {
 
-constexpr int STAGES = 4;
+#ifndef TSP_SMALL_STAGES
+#define TSP_SMALL_STAGES 2
+#endif
+constexpr int STAGES = TSP_SMALL_STAGES;
 constexpr int WARPS = 4;
+#ifndef TSP_SMALL_MAXNS
+#define TSP_SMALL_MAXNS 128
+#endif
+#ifndef TSP_SMALL_MINBLOCKS
+#define TSP_SMALL_MINBLOCKS 1
+#endif
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
 {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async16s(unsigned smem, const void *gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem), "l"(gmem));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -69,7 +82,7 @@ __device__ __forceinline__ int swz(int c, int k)
 }
 
 template <int PREC, int CLS, int NS>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? 6 : 4))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const unsigned int *__restrict__ task_row,
              const int *__restrict__ task_start, const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
              const unsigned char *__restrict__ dB, float *__restrict__ dC)
@@ -95,24 +108,35 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
 #pragma unroll
     for (int i = 0; i < NACC; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
 
+    // Per-lane constants of the gather.  Chunk q = it*32 + lane of a tile is 16-byte chunk c = lane % CPR of row
+    // k = it*KPI + lane/CPR (32 % CPR == 0), so the source column offset and the swizzled destination offset of
+    // every copy are loop invariants: one shuffle, one 32x32->64 multiply-add and the copy per 16 bytes.
+    static_assert(32 % CPR == 0 || CPR % 32 == 0, "chunks per row must divide or be a multiple of the warp size");
+    constexpr int KPI = CPR <= 32 ? 32 / CPR : 1;          // tile rows covered by one warp-wide copy
+    constexpr int ITERS = BN * CPR / 32;
+    const int c_mine = lane % CPR, k_mine = lane / CPR;
+    const unsigned char *gsrc = dB + stripe_bytes + (size_t)c_mine * 16;
+    const unsigned ldb_b = (unsigned)ldb_bytes;
+    const unsigned ring_s = (unsigned)__cvta_generic_to_shared(ring);
+    const unsigned char *a_src = tile_val + (size_t)t0 * Cfg::A_BYTES + lane * 16;
+    const int *idx_ptr = tile_colidx + (size_t)t0 * BN + lane;
     // column index of tile row `lane` for the tile that will be issued next
-    int idx_next = (nt > 0 && lane < BN) ? __ldg(tile_colidx + (size_t)t0 * BN + lane) : 0;
+    int idx_next = (nt > 0 && lane < BN) ? __ldg(idx_ptr) : 0;
 
     auto issue = [&](int i) {
-        unsigned char *st = ring + (i % STAGES) * Cfg::STAGE_BYTES;
-        const unsigned char *a_src = tile_val + (size_t)(t0 + i) * Cfg::A_BYTES;
-        if (lane * 16 < Cfg::A_BYTES) cp_async16(st + lane * 16, a_src + lane * 16);
+        const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
+        if (lane * 16 < Cfg::A_BYTES) cp_async16s(st + lane * 16, a_src);
+        a_src += Cfg::A_BYTES;
         const int idx_mine = idx_next;
 #pragma unroll
-        for (int it = 0; it < (BN * CPR + 31) / 32; it++)
+        for (int it = 0; it < ITERS; it++)
         {
-            const int q = it * 32 + lane;
-            const int k = q / CPR, c = q % CPR;
-            const int col = __shfl_sync(0xffffffffu, idx_mine, k & (BN - 1));
-            if (q < BN * CPR)
-                cp_async16(st + Cfg::A_BYTES + k * RB + swz<RB>(c, k) * 16, dB + (size_t)col * ldb_bytes + stripe_bytes + c * 16);
+            const int k = it * KPI + k_mine;
+            const int col = __shfl_sync(0xffffffffu, idx_mine, k);
+            cp_async16s(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b);
         }
-        if (i + 1 < nt && lane < BN) idx_next = __ldg(tile_colidx + (size_t)(t0 + i + 1) * BN + lane);
+        idx_ptr += BN;
+        if (i + 1 < nt && lane < BN) idx_next = __ldg(idx_ptr);
     };
 
     for (int i = 0; i < STAGES - 1; i++)
@@ -144,16 +168,24 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         }
         else if constexpr (CLS == 1 && PREC == 1)
         {
+            // TF32 has no ldmatrix path, so the output columns of the MMAs are permuted instead: lane group
+            // g = lane/4 owns the W = NS/8 consecutive columns g*W.., and n-block nb uses column g*W + nb of
+            // every group.  A lane then reads its B operands with 16-byte loads (W/4 per K row).
             const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
-            const int k = lane & 3, n = lane >> 2;
+            constexpr int W = NS / 8;
+            const int k = lane & 3, g = lane >> 2;
+            unsigned b0[W], b1[W];
 #pragma unroll
-            for (int nb = 0; nb < NS / 8; nb++)
+            for (int j = 0; j < W / 4; j++)
             {
-                const int chunk = nb * 2 + (n >> 2);
-                const unsigned b0 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(chunk, k) * 16 + (n & 3) * 4);
-                const unsigned b1 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16 + (n & 3) * 4);
-                mma_tf32(acc[nb], a.x, a.y, a.z, a.w, b0, b1);
+                const int chunk = g * (W / 4) + j;
+                const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
+                const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
+                b0[4 * j] = x.x; b0[4 * j + 1] = x.y; b0[4 * j + 2] = x.z; b0[4 * j + 3] = x.w;
+                b1[4 * j] = y.x; b1[4 * j + 1] = y.y; b1[4 * j + 2] = y.z; b1[4 * j + 3] = y.w;
             }
+#pragma unroll
+            for (int nb = 0; nb < W; nb++) mma_tf32(acc[nb], a.x, a.y, a.z, a.w, b0[nb], b1[nb]);
         }
         else if constexpr (CLS == 2 && PREC == 0)
         {
@@ -170,18 +202,23 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         }
         else
         {
+            // same column permutation as the 16-row TF32 kernel: lane group g owns columns g*W .. g*W+W-1 and
+            // MMA mb takes column g*W + 2*mb for its row m = g and g*W + 2*mb + 1 for its row m + 8
             const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
-            const int k = lane & 3, m = lane >> 2;
+            constexpr int W = NS / 8;
+            const int k = lane & 3, g = lane >> 2;
+            unsigned r0[W], r1[W];
 #pragma unroll
-            for (int mb = 0; mb < NS / 16; mb++)
+            for (int j = 0; j < W / 4; j++)
             {
-                const int c0 = mb * 4 + (m >> 2), c1 = c0 + 2;
-                const unsigned a0 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(c0, k) * 16 + (m & 3) * 4);
-                const unsigned a1 = *reinterpret_cast<const unsigned *>(sb + k * RB + swz<RB>(c1, k) * 16 + (m & 3) * 4);
-                const unsigned a2 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(c0, k + 4) * 16 + (m & 3) * 4);
-                const unsigned a3 = *reinterpret_cast<const unsigned *>(sb + (k + 4) * RB + swz<RB>(c1, k + 4) * 16 + (m & 3) * 4);
-                mma_tf32(acc[mb], a0, a1, a2, a3, b.x, b.y);
+                const int chunk = g * (W / 4) + j;
+                const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
+                const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
+                r0[4 * j] = x.x; r0[4 * j + 1] = x.y; r0[4 * j + 2] = x.z; r0[4 * j + 3] = x.w;
+                r1[4 * j] = y.x; r1[4 * j + 1] = y.y; r1[4 * j + 2] = y.z; r1[4 * j + 3] = y.w;
             }
+#pragma unroll
+            for (int mb = 0; mb < W / 2; mb++) mma_tf32(acc[mb], r0[2 * mb], r0[2 * mb + 1], r1[2 * mb], r1[2 * mb + 1], b.x, b.y);
         }
         __syncwarp();
     }
@@ -189,7 +226,27 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
     const size_t ldc = (size_t)ldb;
     float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
-    if constexpr (CLS == 1)
+    if constexpr (CLS == 1 && PREC == 1)
+    {
+        // permuted columns: accumulator (row, n') of n-block nb is C[row][n'*W + nb], n' = (lane%4)*2 + {0,1}
+        constexpr int W = NS / 8;
+        const int r = lane >> 2;
+#pragma unroll
+        for (int half = 0; half < 2; half++)
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+            {
+                float *p = cbase + (size_t)(r + 8 * half) * ldc + ((lane & 3) * 2 + j) * W;
+#pragma unroll
+                for (int q = 0; q < W; q += 4)
+                {
+                    const float v0 = acc[q][half * 2 + j], v1 = acc[q + 1][half * 2 + j], v2 = acc[q + 2][half * 2 + j], v3 = acc[q + 3][half * 2 + j];
+                    if (split) { atomicAdd(p + q, v0); atomicAdd(p + q + 1, v1); atomicAdd(p + q + 2, v2); atomicAdd(p + q + 3, v3); }
+                    else *reinterpret_cast<float4 *>(p + q) = make_float4(v0, v1, v2, v3);
+                }
+            }
+    }
+    else if constexpr (CLS == 1)
     {
         const int r = lane >> 2, c = (lane & 3) * 2;
 #pragma unroll
@@ -205,6 +262,24 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 *reinterpret_cast<float2 *>(p0) = make_float2(acc[nb][0], acc[nb][1]);
                 *reinterpret_cast<float2 *>(p1) = make_float2(acc[nb][2], acc[nb][3]);
+            }
+        }
+    }
+    else if constexpr (PREC == 1)
+    {
+        // transposed block with permuted columns: accumulator (m, n) of MMA mb is C[row n][g*W + 2*mb + (m >= 8)]
+        constexpr int W = NS / 8;
+        const int g = lane >> 2, n = (lane & 3) * 2;
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+        {
+            float *p = cbase + (size_t)(n + j) * ldc + g * W;
+#pragma unroll
+            for (int q = 0; q < W / 2; q += 2)
+            {
+                const float v0 = acc[q][j], v1 = acc[q][2 + j], v2 = acc[q + 1][j], v3 = acc[q + 1][2 + j];
+                if (split) { atomicAdd(p + 2 * q, v0); atomicAdd(p + 2 * q + 1, v1); atomicAdd(p + 2 * q + 2, v2); atomicAdd(p + 2 * q + 3, v3); }
+                else *reinterpret_cast<float4 *>(p + 2 * q) = make_float4(v0, v1, v2, v3);
             }
         }
     }
@@ -257,7 +332,7 @@ template <int PREC, int CLS>
 int launch_width(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)
 {
     if (colB == 32) return launch_one<PREC, CLS, 32>(h, d_b, d_c, colB, s);
-    if (colB % 128 == 0) return launch_one<PREC, CLS, 128>(h, d_b, d_c, colB, s);
+    if (colB % 128 == 0 && TSP_SMALL_MAXNS >= 128) return launch_one<PREC, CLS, 128>(h, d_b, d_c, colB, s);
     return launch_one<PREC, CLS, 64>(h, d_b, d_c, colB, s);
 }
 
@@ -310,7 +385,7 @@ int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int co
 
 void tsp_small_resources(int precision, int cls, int colB, TspKernelResources *out)
 {
-    const int ns = colB == 32 ? 32 : (colB % 128 == 0 ? 128 : 64);
+    const int ns = colB == 32 ? 32 : ((colB % 128 == 0 && TSP_SMALL_MAXNS >= 128) ? 128 : 64);
 #define TSP_RES(P, C)                                                  \
     do {                                                               \
         if (ns == 32) resources_one<P, C, 32>(out);                    \
