@@ -195,7 +195,7 @@ def main():
         return run_reference(args)
 
     import torch
-    from tilespmm_b200 import api
+    from tilespmm_b200 import api, multi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -246,7 +246,7 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         dist.barrier()
         e0.record()
-        dist.broadcast(dB, src=0)
+        multi.broadcast_dense(dB, dist, src=0)
         e1.record()
         torch.cuda.synchronize()
         bcast_ms = e0.elapsed_time(e1)
@@ -288,10 +288,7 @@ def main():
         m.spmm(dB, dC, cb, stream)
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    ms_step = multi.max_over_ranks(ms_total, dist, "cuda") / args.steps
     tflops = 2.0 * nnz * colB / (ms_step * 1e-3) / 1e12
 
     # per-class kernel timing for the roofline of the dominant kernel (CUDA events on the launching stream)
@@ -328,11 +325,9 @@ def main():
         for _ in range(args.e2e_steps):
             api._check(L.tsp_spmm_host(m.h, C.c_void_p(Bnp.ctypes.data), C.c_void_p(Ch.data_ptr()), cb), "tsp_spmm_host")
         torch.cuda.synchronize()
-        dt = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        e2e = {"value": 2.0 * nnz * colB / float(dt.item()) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(Bnp.nbytes), "d2h_bytes_per_step": int(Ch.numel() * 4), "ms_per_step": float(dt.item()) * 1e3}
+        dt = multi.max_over_ranks((time.perf_counter() - t0) / args.e2e_steps, dist, "cuda")
+        e2e = {"value": 2.0 * nnz * colB / dt / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(Bnp.nbytes), "d2h_bytes_per_step": int(Ch.numel() * 4), "ms_per_step": dt * 1e3}
 
     if rank != 0:
         if world > 1:

@@ -107,3 +107,25 @@ def test_shards_agree_with_unsharded_tiling():
         for cls in range(3):
             for w in ("tile_colidx", "tile_val", "panel_row", "orig_row"):
                 np.testing.assert_array_equal(np.concatenate([p.array(cls, w) for p in parts]), full.array(cls, w))
+
+
+def test_shard_boundaries_follow_the_byte_balance_rule():
+    """The library cuts the global panel sequence where tilespmm_b200.multi.shard_cuts says (same cost rule)."""
+    from tilespmm_b200 import api, multi, synth
+    rp, ci, v, shape = synth.rmat_symmetric(14, 16, 78)
+    prec, (g, d), world = 0, (2.0, 1.2), 4
+    full = api.TileMatrix(prec).convert_host(shape, rp, ci, v, g, d)
+    full.info()
+    panels = []
+    for cls in range(3):
+        rows, tp = full.array(cls, "panel_row"), full.array(cls, "tile_ptr")
+        panels += [(int(r), cls, int(n)) for r, n in zip(rows, np.diff(tp))]
+    panels.sort()
+    costs = [multi.panel_cost(n, _orc.CLASSES[cls], _orc.BN(prec, cls), 2) for _, cls, n in panels]
+    cuts = multi.shard_cuts(costs, world)
+    for k in range(world):
+        part = api.TileMatrix(prec).convert_host(shape, rp, ci, v, g, d, shard=(k, world))
+        part.info()
+        want_begin = panels[cuts[k]][0] if cuts[k] < len(panels) else shape[0]
+        want_end = panels[cuts[k + 1]][0] if cuts[k + 1] < len(panels) else shape[0]
+        assert part.row_range == (want_begin, want_end), (k, part.row_range, want_begin, want_end)

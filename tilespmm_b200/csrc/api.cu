@@ -188,8 +188,7 @@ extern "C" int tsp_kernel_info(const tsp_handle *h, int cls, int colB, long long
     TSP_CUDA(cudaSetDevice(h->device));
     TspKernelResources R;
     tsp_kernel_resources(h->precision, cls, colB, &R);
-    const int stripe = cls == 0 ? (colB == 32 ? 32 : (colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64)))
-                                : (colB == 32 ? 32 : (colB % 128 == 0 ? 128 : 64));
+    const int stripe = tsp_stripe_width(cls, colB);
     out6[0] = R.threads; out6[1] = R.registers_per_thread; out6[2] = R.shared_bytes; out6[3] = R.iteration_bytes;
     out6[4] = R.tasks_per_block; out6[5] = colB / stripe;
     return TSP_OK;

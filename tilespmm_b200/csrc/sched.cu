@@ -167,8 +167,7 @@ int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
     int tmax = (max_len + 7) / 8 * 8;
     if (tmax > 128) tmax = 128;
     // one block of these kernels serves tasks_per_block tasks of one stripe
-    const int stripe = cls == 0 ? (colB == 32 ? 32 : (colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64)))
-                                : (colB == 32 ? 32 : (colB % 128 == 0 ? 128 : 64));
+    const int stripe = tsp_stripe_width(cls, colB);
     int cand_th[16], ncand = 0;
     float cand_cost[16];
     long long prev_tasks = -1;

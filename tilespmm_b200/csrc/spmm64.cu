@@ -322,10 +322,13 @@ int launch64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t 
 template <int PREC>
 int launch64_width(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)
 {
-    if (colB == 32) return launch64<PREC, 32>(h, d_b, d_c, colB, s);
-    if (colB % 256 == 0) return launch64<PREC, 256>(h, d_b, d_c, colB, s);
-    if (colB % 128 == 0) return launch64<PREC, 128>(h, d_b, d_c, colB, s);
-    return launch64<PREC, 64>(h, d_b, d_c, colB, s);
+    switch (tsp_stripe_width(0, colB))
+    {
+    case 32: return launch64<PREC, 32>(h, d_b, d_c, colB, s);
+    case 256: return launch64<PREC, 256>(h, d_b, d_c, colB, s);
+    case 128: return launch64<PREC, 128>(h, d_b, d_c, colB, s);
+    default: return launch64<PREC, 64>(h, d_b, d_c, colB, s);
+    }
 }
 
 template <int PREC, int N>
@@ -351,7 +354,7 @@ int tsp_launch_class64(tsp_handle *h, const void *d_b, float *d_c, int colB, cud
 
 void tsp_class64_resources(int precision, int colB, TspKernelResources *out)
 {
-    const int n = colB == 32 ? 32 : (colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64));
+    const int n = tsp_stripe_width(0, colB);
 #define TSP_R64(P)                                   \
     do {                                             \
         if (n == 32) resources64<P, 32>(out);        \

@@ -2,9 +2,8 @@
 //
 // They replace upstream stir_spmm_cuda_kernel_v16*/v8* (src/tilespmm_cuda.h:12-1023) and the launch switches
 // (src/tilespmm_cuda.h:1634-1708).  Differences that matter on B200:
-//   * one warp owns one (task, column stripe) and keeps a STAGES-deep ring of gathered B rows in flight
-//     (upstream: depth 1 for 16-row tiles, none for 8-row tiles), so that the gather is limited by memory
-//     throughput, not by latency;
+//   * one warp owns one (task, column stripe) and keeps a 2- to 6-deep ring of gathered B rows in flight
+//     (upstream: depth 1 for 16-row tiles, none for 8-row tiles) at 16-24 resident warps per SM;
 //   * a stripe is up to 128 columns wide (upstream: 64), so the A tile and the column indices are read
 //     once per 128 columns and a gathered row segment is up to 512 contiguous bytes;
 //   * every global access is a 16-byte cp.async (B rows, A tile) or a full 32-byte sector store (C);
@@ -16,17 +15,11 @@
 namespace
 {
 
-#ifndef TSP_SMALL_STAGES
-#define TSP_SMALL_STAGES 2
-#endif
-constexpr int STAGES = TSP_SMALL_STAGES;
 constexpr int WARPS = 4;
-#ifndef TSP_SMALL_MAXNS
-#define TSP_SMALL_MAXNS 128
-#endif
-#ifndef TSP_SMALL_MINBLOCKS
-#define TSP_SMALL_MINBLOCKS 1
-#endif
+// Ring depth per warp.  Occupancy beats depth on B200 (24 resident warps with 2 stages outrun 12 warps with 4),
+// so the ring only grows while a warp's ring stays within ~9 KB: 2 stages for 128-column stripes, 4 for 64, 6 for 32
+// (narrow stripes also mean small grids, where the per-warp chain of tile latencies is what is left to hide).
+constexpr int ring_stages(int stage_bytes) { return 9216 / stage_bytes < 2 ? 2 : (9216 / stage_bytes > 6 ? 6 : 9216 / stage_bytes); }
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
 {
@@ -69,6 +62,7 @@ struct SmallCfg
     static constexpr int A_BYTES = BM * BN * SZ;       // 512 (16-row) or 256 (8-row)
     static constexpr int B_BYTES = BN * RB;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = ring_stages(STAGE_BYTES);
     static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
     static constexpr int SMEM = WARPS * WARP_BYTES;
 };
@@ -88,7 +82,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
              const unsigned char *__restrict__ dB, float *__restrict__ dC)
 {
     using Cfg = SmallCfg<PREC, CLS, NS>;
-    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR;
+    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * WARPS + warp;
@@ -331,9 +325,12 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
 template <int PREC, int CLS>
 int launch_width(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)
 {
-    if (colB == 32) return launch_one<PREC, CLS, 32>(h, d_b, d_c, colB, s);
-    if (colB % 128 == 0 && TSP_SMALL_MAXNS >= 128) return launch_one<PREC, CLS, 128>(h, d_b, d_c, colB, s);
-    return launch_one<PREC, CLS, 64>(h, d_b, d_c, colB, s);
+    switch (tsp_stripe_width(CLS, colB))
+    {
+    case 32: return launch_one<PREC, CLS, 32>(h, d_b, d_c, colB, s);
+    case 128: return launch_one<PREC, CLS, 128>(h, d_b, d_c, colB, s);
+    default: return launch_one<PREC, CLS, 64>(h, d_b, d_c, colB, s);
+    }
 }
 
 template <int PREC, int CLS, int NS>
@@ -385,7 +382,7 @@ int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int co
 
 void tsp_small_resources(int precision, int cls, int colB, TspKernelResources *out)
 {
-    const int ns = colB == 32 ? 32 : ((colB % 128 == 0 && TSP_SMALL_MAXNS >= 128) ? 128 : 64);
+    const int ns = tsp_stripe_width(cls, colB);
 #define TSP_RES(P, C)                                                  \
     do {                                                               \
         if (ns == 32) resources_one<P, C, 32>(out);                    \

@@ -75,6 +75,15 @@ __host__ __device__ inline int tsp_device_index(int precision, int cls, int r, i
     return cls == 0 ? tsp_umma_index(precision, r, c) : tsp_upstream_index(precision, cls, r, c);
 }
 
+// Width of the column stripe one task unit covers for (class, padded dense width): the 64-row kernel keeps up to
+// 256 accumulator columns in tensor memory, the 16/8-row kernels up to 128 in registers.
+__host__ __device__ inline int tsp_stripe_width(int cls, int colB)
+{
+    if (colB == 32) return 32;
+    if (cls == 0) return colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64);
+    return colB % 128 == 0 ? 128 : 64;
+}
+
 // ---------------------------------------------------------------- handle
 
 struct TspKernelResources  // what the platform probe records per (class, width) kernel
