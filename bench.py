@@ -336,7 +336,7 @@ def main():
         return
 
     cpu = None
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:   # the CPU baseline is timed at N=1 only
         best, n, threads = cpu_csr_spmm_timed(prec, shape, rp, ci, vv, Bv, colB)
         cpu = {"value": 2.0 * nnz * colB / best / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                "sample": f"whole workload, best of {n} passes ({best * 1e3:.1f} ms)"}
@@ -363,7 +363,7 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (key: workload, class); None where no capture exists.
-TRAFFIC = {}
+TRAFFIC = {("c2", 2): 346.9e6, ("c2", 1): 419.8e6, ("c2", 0): 854.8e6}   # profiles/c2_spmm_{8,16,64}row_*.md
 
 if __name__ == "__main__":
     main()

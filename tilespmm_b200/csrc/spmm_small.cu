@@ -51,6 +51,14 @@ __device__ __forceinline__ void mma_tf32(float *d, unsigned a0, unsigned a1, uns
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// K = 4 form: its A operand is two registers that belong to ONE K column, so a lane can feed it straight from one
+// 16-byte shared-memory load (the K = 8 form needs registers from two different tile rows side by side).
+__device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, unsigned b0)
+{
+    asm volatile("mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
+}
+
 template <int PREC, int CLS, int NS>
 struct SmallCfg
 {
@@ -168,18 +176,18 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
             constexpr int W = NS / 8;
             const int k = lane & 3, g = lane >> 2;
-            unsigned b0[W], b1[W];
+            // two K = 4 MMAs per n-block: tile rows 0-3 with (a.x, a.y), rows 4-7 with (a.z, a.w)
 #pragma unroll
             for (int j = 0; j < W / 4; j++)
             {
                 const int chunk = g * (W / 4) + j;
                 const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
                 const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
-                b0[4 * j] = x.x; b0[4 * j + 1] = x.y; b0[4 * j + 2] = x.z; b0[4 * j + 3] = x.w;
-                b1[4 * j] = y.x; b1[4 * j + 1] = y.y; b1[4 * j + 2] = y.z; b1[4 * j + 3] = y.w;
+                mma_tf32_k4(acc[4 * j], a.x, a.y, x.x); mma_tf32_k4(acc[4 * j + 1], a.x, a.y, x.y);
+                mma_tf32_k4(acc[4 * j + 2], a.x, a.y, x.z); mma_tf32_k4(acc[4 * j + 3], a.x, a.y, x.w);
+                mma_tf32_k4(acc[4 * j], a.z, a.w, y.x); mma_tf32_k4(acc[4 * j + 1], a.z, a.w, y.y);
+                mma_tf32_k4(acc[4 * j + 2], a.z, a.w, y.z); mma_tf32_k4(acc[4 * j + 3], a.z, a.w, y.w);
             }
-#pragma unroll
-            for (int nb = 0; nb < W; nb++) mma_tf32(acc[nb], a.x, a.y, a.z, a.w, b0[nb], b1[nb]);
         }
         else if constexpr (CLS == 2 && PREC == 0)
         {
@@ -201,18 +209,17 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
             constexpr int W = NS / 8;
             const int k = lane & 3, g = lane >> 2;
-            unsigned r0[W], r1[W];
+            // two K = 4 MMAs per 16 columns: tile rows 0-3 with b.x, rows 4-7 with b.y; one 16-byte load of a
+            // gathered row yields the A operands (columns 2*mb, 2*mb+1 of the lane's group) of two MMAs
 #pragma unroll
             for (int j = 0; j < W / 4; j++)
             {
                 const int chunk = g * (W / 4) + j;
                 const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
                 const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
-                r0[4 * j] = x.x; r0[4 * j + 1] = x.y; r0[4 * j + 2] = x.z; r0[4 * j + 3] = x.w;
-                r1[4 * j] = y.x; r1[4 * j + 1] = y.y; r1[4 * j + 2] = y.z; r1[4 * j + 3] = y.w;
+                mma_tf32_k4(acc[2 * j], x.x, x.y, b.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, b.x);
+                mma_tf32_k4(acc[2 * j], y.x, y.y, b.y); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, b.y);
             }
-#pragma unroll
-            for (int mb = 0; mb < W / 2; mb++) mma_tf32(acc[mb], r0[2 * mb], r0[2 * mb + 1], r1[2 * mb], r1[2 * mb + 1], b.x, b.y);
         }
         __syncwarp();
     }
