@@ -136,6 +136,13 @@ int tsp_cusparse_baseline(int device, int precision, int m, int k, long long nnz
                           const int *h_colidx, const void *h_val, int n, int ldb, const void *h_b, float *h_c,
                           int warmup, int repeat, double *out3);
 
+/* ---- Matrix Market loader with the semantics of upstream mmio_allinone (src/mmio_highlevel.h:307-480): file order
+ * inside rows, repeated entries kept, symmetric/hermitian files expanded, pattern = 1.0.  The three arrays are
+ * malloc'ed by the callee; release each with tsp_free_host. */
+int tsp_read_mtx(const char *path, int *m, int *n, long long *nnz, int *is_symmetric, int **h_rowptr, int **h_colidx,
+                 float **h_val);
+void tsp_free_host(void *p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -185,6 +185,14 @@ int ref_cusparse(int m, int k, int nnzA, int *rowptr, int *colidx, MAT_VAL_TYPE 
     return got == 3 ? 0 : 3;
 }
 
+// src/mmio_highlevel.h:307-480.  Returns the arrays malloc'ed by upstream; sizes through the out parameters.
+int ref_read_mtx(char *path, int *m, int *n, int *nnz, int *is_symmetric, int **rowptr, int **colidx, MAT_VAL_TYPE **val)
+{
+    return mmio_allinone(m, n, nnz, is_symmetric, rowptr, colidx, val, path);
+}
+
+void ref_free(void *p) { free(p); }
+
 void ref_destroy(void *handle)
 {
     RefHandle *h = (RefHandle *)handle;

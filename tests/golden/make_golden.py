@@ -64,6 +64,20 @@ def main():
             fa = np.asarray(f, dtype=np.float64)
             _orc.Upstream.lib(prec).ref_predict_features(fa.ctypes.data_as(C.c_void_p), C.byref(g), C.byref(d))
             golden["model"].append({"precision": prec, "features": f, "gamma": g.value, "delta": d.value})
+    # Matrix Market loader: upstream mmio_allinone (src/mmio_highlevel.h:307-480) on the fixtures under tests/golden/mtx
+    import ctypes as C
+    import glob
+    L = _orc.Upstream.lib(1)
+    golden["mtx"] = {}
+    for path in sorted(glob.glob(os.path.join(HERE, "mtx", "*.mtx"))):
+        m, n, nnz, sym = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        rp, ci, va = C.POINTER(C.c_int)(), C.POINTER(C.c_int)(), C.POINTER(C.c_float)()
+        rc = L.ref_read_mtx(path.encode(), C.byref(m), C.byref(n), C.byref(nnz), C.byref(sym), C.byref(rp), C.byref(ci), C.byref(va))
+        assert rc == 0, (path, rc)
+        golden["mtx"][os.path.basename(path)] = {"m": m.value, "n": n.value, "nnz": nnz.value, "symmetric": sym.value,
+                                                  "rowptr": [rp[i] for i in range(m.value + 1)],
+                                                  "colidx": [ci[i] for i in range(nnz.value)],
+                                                  "val": [float(va[i]) for i in range(nnz.value)]}
     with open(os.path.join(HERE, "tiling_golden.json"), "w") as fh:
         json.dump(golden, fh, separators=(",", ":"))
     np.savez_compressed(os.path.join(HERE, "tiny_arrays.npz"), **tiny)

@@ -8,7 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtilespmm_b200.so")
-SOURCES = ["api.cu", "convert.cu", "sched.cu", "spmm_small.cu", "spmm64.cu", "model.cu"]
+SOURCES = ["api.cu", "convert.cu", "sched.cu", "spmm_small.cu", "spmm64.cu", "model.cu", "mtx_reader.cpp"]
+BIN = os.path.join(HERE, "bin")
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-w"]
 
@@ -29,7 +30,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(HERE, "build", src.replace(".cu", ".o"))
+        o = os.path.join(HERE, "build", os.path.splitext(src)[0] + ".o")
         objs.append(o)
         if not force and _newer(o, [s] + headers):
             continue
@@ -45,6 +46,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if procs or not os.path.exists(LIB) or force:
         cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcusparse", "-lcudart"]
         subprocess.run(cmd, check=True)
+    # the two drop-in executables (upstream bin/tilespmm_fp16, bin/tilespmm_tf32)
+    os.makedirs(BIN, exist_ok=True)
+    cli = os.path.join(CSRC, "cli_main.cpp")
+    for prec, name in ((0, "tilespmm_fp16"), (1, "tilespmm_tf32")):
+        exe = os.path.join(BIN, name)
+        if force or not _newer(exe, [cli, LIB] + headers):
+            subprocess.run([nvcc, "-std=c++17", "-O2", "-w", f"-DTSP_PRECISION={prec}", cli, "-o", exe, f"-L{HERE}", "-ltilespmm_b200",
+                            "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/..", "-lcudart"], check=True)
     if logs:
         with open(os.path.join(HERE, "build", "ptxas.log"), "w") as fh:
             fh.write("\n".join(logs))
