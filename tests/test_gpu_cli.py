@@ -14,7 +14,8 @@ def write_mtx(path, rows, cols, seed):
     rng = np.random.default_rng(seed)
     ents = {(int(rng.integers(1, rows + 1)), int(rng.integers(1, cols + 1))) for _ in range(rows * 9)}
     with open(path, "w") as f:
-        f.write("%%MatrixMarket matrix coordinate real general\n%d %d %d\n" % (rows, cols, len(ents)))
+        f.write("%" + "%MatrixMarket matrix coordinate real general\n")
+        f.write("%d %d %d\n" % (rows, cols, len(ents)))
         for i, j in sorted(ents, key=lambda e: (e[1], e[0])):      # column-major file order: rows come out unsorted
             f.write("%d %d %.3f\n" % (i, j, rng.normal()))
     return len(ents)
