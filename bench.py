@@ -208,11 +208,24 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    rp, ci, v, shape, cfg, desc = make_workload(args.workload, world, args.scale)
+    on_device = args.workload == "c5"       # ~500 M nonzeros: generated on the GPU, converted from device memory
+    if on_device:
+        cfg = dict(synth.CONFIGS["c5"])
+        scale = args.scale or 24
+        d_rp, d_ci, d_v, shape = synth.rmat_symmetric_device(scale, 16, 1005, values="u01")
+        d_v = d_v.to(torch.float16) if PREC[cfg["precision"]] == 0 else d_v
+        rp = d_rp.cpu().numpy()
+        ci = v = vv = None
+        nnz = int(d_ci.numel())
+        desc = f"c5: symmetric R-MAT scale {scale}, FP16, colB=128 (generated on the GPU)"
+        args.no_cpu = args.no_cusparse = True
+    else:
+        rp, ci, v, shape, cfg, desc = make_workload(args.workload, world, args.scale)
+        nnz = int(ci.size)
     prec, colB = PREC[cfg["precision"]], cfg["colB"]
     cb = api.padded_width(colB)
-    vv = api.to_values(v, prec)
-    nnz = int(ci.size)
+    if not on_device:
+        vv = api.to_values(v, prec)
     scaling = "weak" if args.workload == "c2" else "strong"
 
     # threshold model (upstream src/main.cu:226-247), conversion on the GPU
@@ -224,7 +237,12 @@ def main():
     if args.delta is not None:
         delta = args.delta
     t0 = time.perf_counter()
-    m = api.TileMatrix(prec, local).convert_host(shape, rp, ci, vv, gamma, delta, shard=(rank, world))
+    if on_device:
+        m = api.TileMatrix(prec, local).convert_device(shape, d_rp, d_ci, d_v, nnz, gamma, delta, shard=(rank, world))
+        del d_ci, d_v
+        torch.cuda.empty_cache()
+    else:
+        m = api.TileMatrix(prec, local).convert_host(shape, rp, ci, vv, gamma, delta, shard=(rank, world))
     torch.cuda.synchronize()
     convert_s = time.perf_counter() - t0
     info = m.info()
@@ -232,7 +250,12 @@ def main():
 
     # B: generated on rank 0, broadcast once over NCCL; C: this rank's row slab
     tdt = torch.float16 if prec == 0 else torch.float32
-    if rank == 0:
+    if rank == 0 and on_device:
+        gB = torch.Generator(device="cuda")
+        gB.manual_seed(7)
+        dB = (torch.rand((shape[1], cb), generator=gB, device="cuda", dtype=torch.float32) * 2 - 1).to(tdt)
+        Bv, B_pinned = None, None
+    elif rank == 0:
         Bh = synth.dense_b(shape[1], cb, 1, cfg["b_dist"])
         Bh[:, colB:] = 0
         Bv = api.to_values(Bh, prec).reshape(shape[1], cb)

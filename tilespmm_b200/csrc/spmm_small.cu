@@ -59,6 +59,40 @@ __device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
+#ifndef TSP_SMALL_BULK
+#define TSP_SMALL_BULK 0
+#endif
+// BULK: the gathered rows and the A tile are fetched by the bulk-copy engine (cp.async.bulk, one copy per row
+// segment, completion on an mbarrier per ring slot) instead of per-lane 16-byte cp.async through the load/store
+// path; rows then sit unswizzled in shared memory with a 16-byte pad per row to keep the operand loads conflict-free.
+// Measured on B200 it is not faster for 512-byte row segments (27-point stencil, TF32, 128 columns: 0.131 ms vs
+// 0.129 ms) and much slower for 128-byte segments (R-MAT scale 20, FP16, 64 columns: 0.72 ms vs 0.45 ms), so it is
+// compiled out by default (-DTSP_SMALL_BULK=1 enables it).
+constexpr bool BULK = TSP_SMALL_BULK != 0;
+constexpr unsigned SMALL_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ void mbar_init_s(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_s(unsigned bar, unsigned parity)
+{
+    for (unsigned it = 0; it < SMALL_WAIT_LIMIT; it++)
+    {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 template <int PREC, int CLS, int NS>
 struct SmallCfg
 {
@@ -68,10 +102,11 @@ struct SmallCfg
     static constexpr int RB = NS * SZ;                 // bytes of one gathered row segment
     static constexpr int CPR = RB / 16;                // 16-byte chunks per row
     static constexpr int A_BYTES = BM * BN * SZ;       // 512 (16-row) or 256 (8-row)
-    static constexpr int B_BYTES = BN * RB;
+    static constexpr int RBS = BULK ? RB + 16 : RB;    // row stride in shared memory
+    static constexpr int B_BYTES = BN * RBS;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = ring_stages(STAGE_BYTES);
-    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES + (BULK ? 64 : 0);   // + one mbarrier per slot
     static constexpr int SMEM = WARPS * WARP_BYTES;
 };
 
@@ -87,10 +122,10 @@ template <int PREC, int CLS, int NS>
 __global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? 6 : 4))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const unsigned int *__restrict__ task_row,
              const int *__restrict__ task_start, const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
-             const unsigned char *__restrict__ dB, float *__restrict__ dC)
+             const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err)
 {
     using Cfg = SmallCfg<PREC, CLS, NS>;
-    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES;
+    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES, RBS = Cfg::RBS;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * WARPS + warp;
@@ -125,33 +160,75 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     // column index of tile row `lane` for the tile that will be issued next
     int idx_next = (nt > 0 && lane < BN) ? __ldg(idx_ptr) : 0;
 
+    const unsigned bars = ring_s + STAGES * Cfg::STAGE_BYTES;
+    if (BULK)
+    {
+        if (lane == 0)
+        {
+            for (int q = 0; q < STAGES; q++) mbar_init_s(bars + 8 * q, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncwarp();
+    }
+    const unsigned char *a_tile = tile_val + (size_t)t0 * Cfg::A_BYTES;
+    const unsigned char *grow = dB + stripe_bytes;
+
     auto issue = [&](int i) {
         const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
-        if (lane * 16 < Cfg::A_BYTES) cp_async16s(st + lane * 16, a_src);
-        a_src += Cfg::A_BYTES;
-        const int idx_mine = idx_next;
-#pragma unroll
-        for (int it = 0; it < ITERS; it++)
+        if (BULK)
         {
-            const int k = it * KPI + k_mine;
-            const int col = __shfl_sync(0xffffffffu, idx_mine, k);
-            cp_async16s(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b);
+            // lane k < BN fetches gathered row k (RB contiguous bytes of B), lane BN the A tile; lane 0 arms the slot
+            const unsigned bar = bars + 8 * (i % STAGES);
+            if (lane == 0) mbar_expect_tx(bar, Cfg::A_BYTES + BN * RB);
+            if (lane < BN) bulk_g2s(st + Cfg::A_BYTES + lane * RBS, grow + (unsigned long long)(unsigned)idx_next * ldb_b, RB, bar);
+            else if (lane == BN) bulk_g2s(st, a_tile, Cfg::A_BYTES, bar);
+            a_tile += Cfg::A_BYTES;
+        }
+        else
+        {
+            if (lane * 16 < Cfg::A_BYTES) cp_async16s(st + lane * 16, a_src);
+            a_src += Cfg::A_BYTES;
+            const int idx_mine = idx_next;
+#pragma unroll
+            for (int it = 0; it < ITERS; it++)
+            {
+                const int k = it * KPI + k_mine;
+                const int col = __shfl_sync(0xffffffffu, idx_mine, k);
+                cp_async16s(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b);
+            }
         }
         idx_ptr += BN;
         if (i + 1 < nt && lane < BN) idx_next = __ldg(idx_ptr);
     };
+    // byte offset of 16-byte chunk `chunk` of gathered row k inside the B part of a slot
+    auto boff = [&](int k, int chunk) -> int { return BULK ? k * RBS + chunk * 16 : k * RB + swz<RB>(chunk, k) * 16; };
 
+    bool ok = true;
     for (int i = 0; i < STAGES - 1; i++)
     {
         if (i < nt) issue(i);
-        cp_async_commit();
+        if (!BULK) cp_async_commit();
     }
     for (int i = 0; i < nt; i++)
     {
         if (i + STAGES - 1 < nt) issue(i + STAGES - 1);
-        cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        __syncwarp();
+        if (BULK)
+        {
+            ok = __all_sync(0xffffffffu, mbar_wait_s(bars + 8 * (i % STAGES), (i / STAGES) & 1));
+            if (!ok)
+            {
+                // give the copies still in flight one more bounded chance to land, report, and stop
+                if (lane == 0) atomicExch(err, 2);
+                for (int q = i; q < nt && q < i + STAGES; q++) mbar_wait_s(bars + 8 * (q % STAGES), (q / STAGES) & 1);
+                break;
+            }
+        }
+        else
+        {
+            cp_async_commit();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+        }
         const unsigned char *st = ring + (i % STAGES) * Cfg::STAGE_BYTES;
         const unsigned char *sb = st + Cfg::A_BYTES;
         if constexpr (CLS == 1 && PREC == 0)
@@ -163,7 +240,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 const int chunk = nb + (lane >> 4);
                 unsigned r0, r1, r2, r3;
-                ldmatrix_x4_trans(r0, r1, r2, r3, sb + k * RB + swz<RB>(chunk, k) * 16);
+                ldmatrix_x4_trans(r0, r1, r2, r3, sb + boff(k, chunk));
                 mma_f16(acc[nb], a.x, a.y, a.z, a.w, r0, r1);
                 mma_f16(acc[nb + 1], a.x, a.y, a.z, a.w, r2, r3);
             }
@@ -181,8 +258,8 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             for (int j = 0; j < W / 4; j++)
             {
                 const int chunk = g * (W / 4) + j;
-                const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
-                const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
+                const uint4 x = *reinterpret_cast<const uint4 *>(sb + boff(k, chunk));
+                const uint4 y = *reinterpret_cast<const uint4 *>(sb + boff(k + 4, chunk));
                 mma_tf32_k4(acc[4 * j], a.x, a.y, x.x); mma_tf32_k4(acc[4 * j + 1], a.x, a.y, x.y);
                 mma_tf32_k4(acc[4 * j + 2], a.x, a.y, x.z); mma_tf32_k4(acc[4 * j + 3], a.x, a.y, x.w);
                 mma_tf32_k4(acc[4 * j], a.z, a.w, y.x); mma_tf32_k4(acc[4 * j + 1], a.z, a.w, y.y);
@@ -198,7 +275,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 const int chunk = mb * 2 + ((lane >> 3) & 1);
                 unsigned a0, a1, a2, a3;
-                ldmatrix_x4_trans(a0, a1, a2, a3, sb + k * RB + swz<RB>(chunk, k) * 16);
+                ldmatrix_x4_trans(a0, a1, a2, a3, sb + boff(k, chunk));
                 mma_f16(acc[mb], a0, a1, a2, a3, b.x, b.y);
             }
         }
@@ -215,8 +292,8 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             for (int j = 0; j < W / 4; j++)
             {
                 const int chunk = g * (W / 4) + j;
-                const uint4 x = *reinterpret_cast<const uint4 *>(sb + k * RB + swz<RB>(chunk, k) * 16);
-                const uint4 y = *reinterpret_cast<const uint4 *>(sb + (k + 4) * RB + swz<RB>(chunk, k + 4) * 16);
+                const uint4 x = *reinterpret_cast<const uint4 *>(sb + boff(k, chunk));
+                const uint4 y = *reinterpret_cast<const uint4 *>(sb + boff(k + 4, chunk));
                 mma_tf32_k4(acc[2 * j], x.x, x.y, b.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, b.x);
                 mma_tf32_k4(acc[2 * j], y.x, y.y, b.y); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, b.y);
             }
@@ -224,6 +301,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         __syncwarp();
     }
 
+    if (!ok) return;
     // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
     const size_t ldc = (size_t)ldb;
     float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
@@ -323,7 +401,7 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
     const int grid = (int)((units + WARPS - 1) / WARPS);
     if (grid == 0) return TSP_OK;
     kern<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_row, c.d_task_start, c.d_tile_colidx,
-                                            (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c);
+                                            (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error);
     TSP_CUDA(cudaGetLastError());
     h->launches++;
     return TSP_OK;

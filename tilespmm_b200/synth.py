@@ -85,6 +85,47 @@ def rmat_symmetric(scale: int = 20, edge_factor: int = 16, seed: int = 1003, val
     return np.cumsum(rowptr).astype(np.int32), cols.astype(np.int32), vals, (n, n)
 
 
+def rmat_symmetric_device(scale: int, edge_factor: int, seed: int, values: str = "one", abcd=(0.57, 0.19, 0.19, 0.05),
+                          device="cuda"):
+    """The same R-MAT law generated on the GPU with torch (configuration 5 has ~500 M nonzeros: too slow on the host).
+    Returns device tensors (rowptr int32[n+1], colidx int32[nnz], values float32[nnz]) and the shape.  Deterministic for
+    a given seed on a given GPU model (torch Philox generator), so every rank of a multi-GPU run builds the same matrix."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    n = 1 << scale
+    m = edge_factor * n
+    a, b, c, _ = abcd
+    src = torch.zeros(m, dtype=torch.int64, device=device)
+    dst = torch.zeros(m, dtype=torch.int64, device=device)
+    for _level in range(scale):
+        u = torch.rand(m, generator=g, device=device)
+        right = ((u >= a) & (u < a + b)) | (u >= a + b + c)
+        down = u >= a + b
+        src = (src << 1) | down
+        dst = (dst << 1) | right
+        del u, right, down
+    keep = src != dst
+    src, dst = src[keep], dst[keep]
+    del keep
+    keys = torch.cat([src * n + dst, dst * n + src])
+    del src, dst
+    keys = torch.unique(keys)
+    rows = torch.div(keys, n, rounding_mode="floor")
+    cols = (keys - rows * n).to(torch.int32)
+    del keys
+    counts = torch.bincount(rows, minlength=n)
+    del rows
+    rowptr = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    rowptr[1:] = torch.cumsum(counts, 0)
+    nnz = int(rowptr[-1].item())
+    if values == "one":
+        vals = torch.ones(nnz, dtype=torch.float32, device=device)
+    else:
+        vals = 1.0 - torch.rand(nnz, generator=g, device=device)
+    return rowptr.to(torch.int32), cols, vals, (n, n)
+
+
 def mixed_density(n: int = 524288, seed: int = 1004, dense_fraction: float = 0.1, blocks_per_panel: int = 4,
                   density: float = 0.5, sparse_per_row: int = 4):
     """Config 4: a random ``dense_fraction`` of the 64-row panels hold ``blocks_per_panel`` 64x64 blocks of
