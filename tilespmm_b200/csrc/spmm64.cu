@@ -6,7 +6,7 @@
 // (upstream: once per 64).  Roles:
 //   warps 0-3  producers: gather the B rows named by tile_colidx with 16-byte cp.async into a STAGES-deep ring,
 //              writing the swizzled MN-major operand layout tcgen05.mma reads, plus the A tile, which
-//              the conversion already stores in the K-major core-matrix order (a straight 4 KB copy);
+//              the conversion already stores in the K-major core-matrix order (one 4 KB cp.async.bulk per tile);
 //              afterwards they are the epilogue: tcgen05.ld of the 64 x N FP32 accumulator -> C.
 //   warp 4     allocates tensor memory; one elected lane issues two tcgen05.mma (M=64, N=stripe, K=16 FP16 /
 //              K=8 TF32) per tile and releases ring slots with tcgen05.commit.
@@ -70,6 +70,16 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
 __device__ __forceinline__ void mbar_arrive(unsigned bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// one bulk copy (the copy engine, no per-thread work): global -> shared, completion counted in bytes on the mbarrier
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // bounded wait: false when the phase did not complete within WAIT_LIMIT polls
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity)
@@ -147,7 +157,7 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
 
     if (tid == 0)
     {
-        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, PRODUCER_WARPS); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, PRODUCER_WARPS + 1); mbar_init(bar_empty + 8 * s, 1); }
         mbar_init(bar_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -171,7 +181,7 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
         const int c_mine = tid % C::CPR, k_mine = tid / C::CPR;
         const unsigned char *gsrc = dB + (size_t)stripe * C::RB + (size_t)c_mine * 16;
         const int *idx_ptr = tile_colidx + (size_t)t0 * C::BNK + k_mine;
-        const unsigned char *a_src = tile_val + (size_t)t0 * C::A_BYTES + tid * 16;
+        const unsigned char *a_src = tile_val + (size_t)t0 * C::A_BYTES;
         int cols_next[C::B_ITERS];
         unsigned dst_off[C::B_ITERS];
 #pragma unroll
@@ -196,8 +206,13 @@ k_spmm64(int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ ta
             if (i >= S) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1));  // warp-uniform outcome
             if (!ok) break;
             const unsigned st = ring + s * C::STAGE_BYTES;
-#pragma unroll
-            for (int q = 0; q < C::A_ITERS; q++) cp_async16(st + (q * (PRODUCER_WARPS * 32) + tid) * 16, a_src + q * (PRODUCER_WARPS * 32) * 16);
+            // the A tile is already in operand order in global memory: one 4 KB bulk copy, whose bytes are
+            // counted on the slot's full barrier together with the producer warps' arrivals
+            if (tid == 0)
+            {
+                mbar_expect_tx(bar_full + 8 * s, C::A_BYTES);
+                bulk_g2s(st, a_src, C::A_BYTES, bar_full + 8 * s);
+            }
             a_src += C::A_BYTES;
 #pragma unroll
             for (int it = 0; it < C::B_ITERS; it++)
