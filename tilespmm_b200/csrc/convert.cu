@@ -570,8 +570,9 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         for (int s = 0; s < nseq; s++)
         {
             const int k = h_seq_cls[s], bm = tsp_bm(k), bn = tsp_bn(prec, k);
-            // bytes of one tile (values + indices + gathered rows of a 128-wide B) plus the C rows of the panel
-            prefix[s + 1] = prefix[s] + (double)h_seq_tiles[s] * (bm * bn * vsz + bn * 4 + bn * 128 * vsz) + bm * 128 * 4.0;
+            // bytes of one tile (values + indices + gathered rows of a 128-wide B) plus the C rows of the panel and a
+            // fixed 12 KB per panel: measured on R-MAT scale 24, starting a task costs about as much as 3 more tiles
+            prefix[s + 1] = prefix[s] + (double)h_seq_tiles[s] * (bm * bn * vsz + bn * 4 + bn * 128 * vsz) + bm * 128 * 4.0 + 12288.0;
         }
         auto cut = [&](int g) {
             const double want = prefix[nseq] * g / shard_count;

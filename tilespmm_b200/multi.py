@@ -12,8 +12,9 @@ import numpy as np
 
 
 def panel_cost(tiles: int, bm: int, bn: int, value_bytes: int) -> float:
-    """Bytes one panel moves per SpMM at a 128-column B: tile values + column indices + gathered rows, plus its C rows."""
-    return tiles * (bm * bn * value_bytes + bn * 4 + bn * 128 * value_bytes) + bm * 128 * 4.0
+    """Bytes one panel moves per SpMM at a 128-column B: tile values + column indices + gathered rows, plus its C rows,
+    plus a fixed 12 KB that stands for the start-up of a task (measured: about three tile-times)."""
+    return tiles * (bm * bn * value_bytes + bn * 4 + bn * 128 * value_bytes) + bm * 128 * 4.0 + 12288.0
 
 
 def shard_cuts(costs, world: int):
