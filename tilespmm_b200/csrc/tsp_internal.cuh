@@ -140,4 +140,3 @@ int tsp_launch_class64(tsp_handle *h, const void *d_b, float *d_c, int colB, cud
 int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
 void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);
-int tsp_spmm64_init(tsp_handle *h);
