@@ -130,3 +130,16 @@ def test_upstream_driver_mirror_and_cusparse_baseline():
         out3, c2 = api.cusparse_baseline(prec, shape, rp, ci, vv, Bv, 40, warmup=2, repeat=5)
         assert out6[4] > 0 and out6[5] > 0 and out3[1] > 0
         assert np.abs(c[:, :40] - c2).max() <= 1e-3
+
+
+def test_tma_gather4_variant_of_the_64_row_kernel():
+    """The 64-row kernel has a second producer: TMA tile::gather4 loads instead of cp.async (TSP_SPMM64=tma, chosen once
+    per process).  Run the 64-row parity cases of this file in a child process with that variant."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, TSP_SPMM64="tma")
+    here = os.path.abspath(__file__)
+    r = subprocess.run([sys.executable, "-m", "pytest", here, "-x", "-q", "-m", "gpu", "-k",
+                        "(gd0 or exact or split) and not tma_gather4"], env=env, capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

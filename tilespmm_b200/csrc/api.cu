@@ -3,6 +3,7 @@
 // baseline that mirrors upstream cusparse_spmm_all (src/main.cu:16-134).
 #include <cusparse.h>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 #include <sys/time.h>
 
@@ -226,7 +227,10 @@ static int ensure_schedules(tsp_handle *h, int colB)
 
 static int launch_class(tsp_handle *h, int k, const void *d_b, float *d_c, int colB, cudaStream_t s)
 {
-    return k == 0 ? tsp_launch_class64(h, d_b, d_c, colB, s) : tsp_launch_small(h, k, d_b, d_c, colB, s);
+    if (k != 0) return tsp_launch_small(h, k, d_b, d_c, colB, s);
+    static int use_tma = -1;   // TSP_SPMM64=tma selects the TMA gather4 producer instead of the (faster) cp.async producers
+    if (use_tma < 0) { const char *e = getenv("TSP_SPMM64"); use_tma = (e && strcmp(e, "tma") == 0) ? 1 : 0; }
+    return use_tma ? tsp_launch_class64_tma(h, d_b, d_c, colB, s) : tsp_launch_class64(h, d_b, d_c, colB, s);
 }
 
 static int spmm_on(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s)

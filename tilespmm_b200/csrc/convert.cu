@@ -427,6 +427,7 @@ void tsp_free_tiles(tsp_handle *h)
         c.BN = tsp_bn(h->precision, k);
     }
     h->converted = false;
+    h->bmap_ptr = nullptr;
 }
 
 int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst)

@@ -125,6 +125,10 @@ struct tsp_handle
     void *stage_b = nullptr;          // device staging of the host-buffer entry points
     float *stage_c = nullptr;
     size_t stage_b_bytes = 0, stage_c_bytes = 0;
+    // tensor map over B for the gather4 loads of the 64-row kernel, rebuilt when B's address or width changes
+    alignas(64) unsigned char bmap[128];
+    const void *bmap_ptr = nullptr;
+    int bmap_cols = 0, bmap_box = 0;
 };
 
 // ---------------------------------------------------------------- cross-TU entry points
@@ -137,6 +141,7 @@ int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst);
 // class kernels; C is addressed relative to row_begin.  count_only != 0 skips the launch and only reports
 // how many launches the call would make.
 int tsp_launch_class64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s);
+int tsp_launch_class64_tma(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
 void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);
