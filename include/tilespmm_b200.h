@@ -112,6 +112,11 @@ long long tsp_c_rows(const tsp_handle *h);
 /* Same, with host buffers: copies B to the device, runs, copies the first rowA rows of C back
  * (upstream src/csr2tile.h:839-842, 1020-1032). */
 int tsp_spmm_host(tsp_handle *h, const void *h_b, float *h_c, int colB_padded);
+/* The same in two steps, for callers that stream many right-hand sides: _async starts upload, kernels and download in
+ * staging slot 0 or 1 and returns; _wait blocks until C of that slot is in h_c.  Alternating the slots overlaps the
+ * upload of one call with the download of the previous one.  Buffers must stay valid (ideally pinned) until _wait. */
+int tsp_spmm_host_async(tsp_handle *h, const void *h_b, float *h_c, int colB_padded, int slot);
+int tsp_spmm_host_wait(tsp_handle *h, int slot);
 
 /* Kernel launches issued by tsp_spmm so far (all classes, including the clearing kernel). */
 long long tsp_launch_count(const tsp_handle *h);

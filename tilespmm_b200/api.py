@@ -46,6 +46,8 @@ def lib() -> C.CDLL:
         L.tsp_c_rows.restype = ll
         L.tsp_c_rows.argtypes = [vp]
         L.tsp_spmm_host.argtypes = [vp, vp, vp, i]
+        L.tsp_spmm_host_async.argtypes = [vp, vp, vp, i, i]
+        L.tsp_spmm_host_wait.argtypes = [vp, i]
         L.tsp_launch_count.restype = ll
         L.tsp_launch_count.argtypes = [vp]
         L.tsp_algorithmic_bytes.argtypes = [vp, i, i, vp]

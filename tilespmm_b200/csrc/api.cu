@@ -90,7 +90,14 @@ extern "C" int tsp_destroy(tsp_handle *h)
     if (h->t0) cudaEventDestroy(h->t0);
     if (h->t1) cudaEventDestroy(h->t1);
     cudaFree(h->d_error);
-    cudaFree(h->stage_b); cudaFree(h->stage_c);
+    for (int i = 0; i < 2; i++)
+    {
+        cudaFree(h->stage_b[i]); cudaFree(h->stage_c[i]);
+        if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+        if (h->ev_cmp[i]) cudaEventDestroy(h->ev_cmp[i]);
+        if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+    }
+    if (h->s_in) { cudaStreamDestroy(h->s_in); cudaStreamDestroy(h->s_cmp); cudaStreamDestroy(h->s_out); }
     delete h;
     return TSP_OK;
 }
@@ -277,37 +284,76 @@ extern "C" int tsp_spmm(tsp_handle *h, const void *d_b, float *d_c, int colB, vo
 }
 
 // device staging buffers of the host-buffer entry points; they grow on demand and live as long as the handle
-static int ensure_staging(tsp_handle *h, size_t b_bytes, size_t c_bytes)
+static int ensure_staging(tsp_handle *h, int slot, size_t b_bytes, size_t c_bytes)
 {
-    if (b_bytes > h->stage_b_bytes)
+    if (!h->s_in)
     {
-        cudaFree(h->stage_b); h->stage_b = nullptr; h->stage_b_bytes = 0;
-        TSP_CUDA(cudaMalloc(&h->stage_b, b_bytes));
-        h->stage_b_bytes = b_bytes;
+        TSP_CUDA(cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking));
+        TSP_CUDA(cudaStreamCreateWithFlags(&h->s_cmp, cudaStreamNonBlocking));
+        TSP_CUDA(cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++)
+        {
+            TSP_CUDA(cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+            TSP_CUDA(cudaEventCreateWithFlags(&h->ev_cmp[i], cudaEventDisableTiming));
+            TSP_CUDA(cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+        }
     }
-    if (c_bytes > h->stage_c_bytes)
+    if (b_bytes > h->stage_b_bytes[slot])
     {
-        cudaFree(h->stage_c); h->stage_c = nullptr; h->stage_c_bytes = 0;
-        TSP_CUDA(cudaMalloc((void **)&h->stage_c, c_bytes));
-        h->stage_c_bytes = c_bytes;
+        cudaFree(h->stage_b[slot]); h->stage_b[slot] = nullptr; h->stage_b_bytes[slot] = 0;
+        TSP_CUDA(cudaMalloc(&h->stage_b[slot], b_bytes));
+        h->stage_b_bytes[slot] = b_bytes;
+    }
+    if (c_bytes > h->stage_c_bytes[slot])
+    {
+        cudaFree(h->stage_c[slot]); h->stage_c[slot] = nullptr; h->stage_c_bytes[slot] = 0;
+        TSP_CUDA(cudaMalloc((void **)&h->stage_c[slot], c_bytes));
+        h->stage_c_bytes[slot] = c_bytes;
     }
     return TSP_OK;
 }
 
-extern "C" int tsp_spmm_host(tsp_handle *h, const void *h_b, float *h_c, int colB)
+// Starts one SpMM with host buffers in staging slot 0 or 1 and returns without waiting: upload of B on the upload
+// stream, kernels on the compute stream, download of C on the download stream, chained by events.  A caller that
+// alternates the slots overlaps the upload of call i+1 with the download of call i.  h_b and h_c must stay valid
+// (and should be pinned) until tsp_spmm_host_wait(h, slot) has returned.
+extern "C" int tsp_spmm_host_async(tsp_handle *h, const void *h_b, float *h_c, int colB, int slot)
 {
-    if (!h || !h_b || !h_c) { tsp_set_error("spmm_host: null argument"); return TSP_EINVAL; }
-    if (!h->converted) { tsp_set_error("spmm_host: convert first"); return TSP_ESTATE; }
+    if (!h || !h_b || !h_c || slot < 0 || slot > 1) { tsp_set_error("spmm_host_async: bad argument"); return TSP_EINVAL; }
+    if (!h->converted) { tsp_set_error("spmm_host_async: convert first"); return TSP_ESTATE; }
+    if (h->slot_busy[slot]) { tsp_set_error("spmm_host_async: slot %d is still in flight; call tsp_spmm_host_wait first", slot); return TSP_ESTATE; }
     TSP_TRY(check_width(colB));
     TSP_CUDA(cudaSetDevice(h->device));
     const size_t vsz = h->precision ? 4 : 2;
     const size_t b_bytes = (size_t)h->colA * colB * vsz, c_bytes = (size_t)tsp_c_rows(h) * colB * 4;
-    TSP_TRY(ensure_staging(h, b_bytes, c_bytes));
-    TSP_CUDA(cudaMemcpyAsync(h->stage_b, h_b, b_bytes, cudaMemcpyHostToDevice, 0));
-    TSP_TRY(tsp_spmm(h, h->stage_b, h->stage_c, colB, nullptr));
-    TSP_CUDA(cudaMemcpyAsync(h_c, h->stage_c, (size_t)(h->row_end - h->row_begin) * colB * 4, cudaMemcpyDeviceToHost, 0));
-    TSP_CUDA(cudaStreamSynchronize(0));
+    TSP_TRY(ensure_staging(h, slot, b_bytes, c_bytes));
+    TSP_TRY(ensure_schedules(h, colB));
+    TSP_CUDA(cudaMemcpyAsync(h->stage_b[slot], h_b, b_bytes, cudaMemcpyHostToDevice, h->s_in));
+    TSP_CUDA(cudaEventRecord(h->ev_in[slot], h->s_in));
+    TSP_CUDA(cudaStreamWaitEvent(h->s_cmp, h->ev_in[slot], 0));
+    TSP_TRY(spmm_on(h, h->stage_b[slot], h->stage_c[slot], colB, h->s_cmp));
+    TSP_CUDA(cudaEventRecord(h->ev_cmp[slot], h->s_cmp));
+    TSP_CUDA(cudaStreamWaitEvent(h->s_out, h->ev_cmp[slot], 0));
+    TSP_CUDA(cudaMemcpyAsync(h_c, h->stage_c[slot], (size_t)(h->row_end - h->row_begin) * colB * 4, cudaMemcpyDeviceToHost, h->s_out));
+    TSP_CUDA(cudaEventRecord(h->ev_out[slot], h->s_out));
+    h->slot_busy[slot] = true;
+    return TSP_OK;
+}
+
+extern "C" int tsp_spmm_host_wait(tsp_handle *h, int slot)
+{
+    if (!h || slot < 0 || slot > 1) { tsp_set_error("spmm_host_wait: bad argument"); return TSP_EINVAL; }
+    if (!h->slot_busy[slot]) return TSP_OK;
+    TSP_CUDA(cudaSetDevice(h->device));
+    TSP_CUDA(cudaEventSynchronize(h->ev_out[slot]));
+    h->slot_busy[slot] = false;
     return check_device_error(h);
+}
+
+extern "C" int tsp_spmm_host(tsp_handle *h, const void *h_b, float *h_c, int colB)
+{
+    TSP_TRY(tsp_spmm_host_async(h, h_b, h_c, colB, 0));
+    return tsp_spmm_host_wait(h, 0);
 }
 
 extern "C" int tsp_algorithmic_bytes(const tsp_handle *h, int cls, int colB, double *b3)

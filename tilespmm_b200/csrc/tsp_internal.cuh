@@ -122,9 +122,14 @@ struct tsp_handle
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     long long launches = 0;
     int *d_error = nullptr;           // device-side error flag (bounded waits)
-    void *stage_b = nullptr;          // device staging of the host-buffer entry points
-    float *stage_c = nullptr;
-    size_t stage_b_bytes = 0, stage_c_bytes = 0;
+    // device staging of the host-buffer entry points: two slots, so that the upload of one call overlaps the
+    // download of the previous one (PCIe is full duplex); one stream per direction plus a compute stream
+    void *stage_b[2] = {nullptr, nullptr};
+    float *stage_c[2] = {nullptr, nullptr};
+    size_t stage_b_bytes[2] = {0, 0}, stage_c_bytes[2] = {0, 0};
+    cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_cmp[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+    bool slot_busy[2] = {false, false};
     // tensor map over B for the gather4 loads of the 64-row kernel, rebuilt when B's address or width changes
     alignas(64) unsigned char bmap[128];
     const void *bmap_ptr = nullptr;
