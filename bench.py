@@ -132,6 +132,7 @@ def cpu_csr_spmm_timed(prec, shape, rp, ci, vv, Bv, colB, budget_s=12.0):
     """The CPU baseline: the checker's OpenMP CSR SpMM on all host threads, best of a few passes."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import _orc
+    _orc.Orc.lib().orc_set_threads(os.cpu_count() or 1)
     best, t_total, n = None, 0.0, 0
     while n < 2 or (t_total < budget_s and n < 8):
         t0 = time.perf_counter()
@@ -158,6 +159,7 @@ def run_reference(args):
     vv = api.to_values(v, prec)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import _orc
+    _orc.Orc.lib().orc_set_threads(os.cpu_count() or 1)      # torchrun sets OMP_NUM_THREADS=1; use every host core
     for _ in range(args.warmup):
         _orc.spmm_csr(prec, shape, rp, ci, vv, Bv, colB)
     t0 = time.perf_counter()
@@ -330,6 +332,11 @@ def main():
                     "unit": "GB/s", "frac": ach / peak, "frac_of_nominal_8TBs": ach / 8000.0, "traffic": TRAFFIC.get((args.workload, dom)),
                     "algorithmic_bytes": {"a_tiles": float(b3[0]), "b_gathered": float(b3[1]), "c": float(b3[2])},
                     "kernel_ms": cls_ms[dom]}
+        if roofline["traffic"]:
+            # what HBM itself sees (ncu DRAM bytes of one launch): the gathered B rows are mostly L2 hits, which is
+            # why the algorithmic fraction above exceeds 1
+            roofline["dram_gbs"] = roofline["traffic"] / (cls_ms[dom] * 1e-3) / 1e9
+            roofline["dram_frac"] = roofline["dram_gbs"] / peak
     all_bytes = float(m.algorithmic_bytes(cb).sum())
 
     # end to end through the C ABI with host buffers: H2D of B, kernels, D2H of C inside the timed region

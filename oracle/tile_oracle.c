@@ -508,3 +508,6 @@ void orc_spmm_csr(int precision, int trunc, int row0, int row1, const int *rowpt
 }
 
 int orc_num_threads(void) { return omp_get_max_threads(); }
+
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline is meant to use every host core. */
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }

@@ -43,6 +43,8 @@ extern "C" int tsp_features_from_csr(int rows, int cols, long long nnz, const in
     return 1;
 }
 
+static int create_resources(tsp_handle *h);
+
 extern "C" int tsp_create(tsp_handle **out, int device, int precision)
 {
     if (!out || (precision != 0 && precision != 1)) { tsp_set_error("create: bad argument"); return TSP_EINVAL; }
@@ -56,12 +58,20 @@ extern "C" int tsp_create(tsp_handle **out, int device, int precision)
     }
     tsp_handle *h = new tsp_handle();
     h->device = device; h->precision = precision;
+    const int rc = create_resources(h);
+    if (rc != TSP_OK) { tsp_destroy(h); return rc; }
+    *out = h;
+    return TSP_OK;
+}
+
+static int create_resources(tsp_handle *h)
+{
+    const int device = h->device, precision = h->precision;
     TSP_CUDA(cudaSetDevice(device));
     TSP_CUDA(cudaGetDeviceProperties(&h->prop, device));
     if (h->prop.major != 10)
     {
         tsp_set_error("create: device %d is sm_%d%d; this library is built for sm_100a only", device, h->prop.major, h->prop.minor);
-        delete h;
         return TSP_EDEVICE;
     }
     for (int k = 0; k < 3; k++) { h->cls[k].BM = tsp_bm(k); h->cls[k].BN = tsp_bn(precision, k); }
@@ -75,7 +85,6 @@ extern "C" int tsp_create(tsp_handle **out, int device, int precision)
     TSP_CUDA(cudaEventCreate(&h->t1));
     TSP_CUDA(cudaMalloc((void **)&h->d_error, 4));
     TSP_CUDA(cudaMemset(h->d_error, 0, 4));
-    *out = h;
     return TSP_OK;
 }
 
