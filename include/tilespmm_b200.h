@@ -141,6 +141,12 @@ int tsp_cusparse_baseline(int device, int precision, int m, int k, long long nnz
                           const int *h_colidx, const void *h_val, int n, int ldb, const void *h_b, float *h_c,
                           int warmup, int repeat, double *out3);
 
+/* ---- tile cache on disk (no upstream counterpart: upstream converts on every run).  tsp_save writes the converted
+ * matrix of the handle (all classes, shard limits included) to one binary file; tsp_load restores it into a handle of
+ * the same precision, replacing whatever it held, without touching the CSR again. */
+int tsp_save(const tsp_handle *h, const char *path);
+int tsp_load(tsp_handle *h, const char *path);
+
 /* ---- Matrix Market loader with the semantics of upstream mmio_allinone (src/mmio_highlevel.h:307-480): file order
  * inside rows, repeated entries kept, symmetric/hermitian files expanded, pattern = 1.0.  The three arrays are
  * malloc'ed by the callee; release each with tsp_free_host. */

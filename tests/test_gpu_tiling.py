@@ -129,3 +129,31 @@ def test_shard_boundaries_follow_the_byte_balance_rule():
         want_begin = panels[cuts[k]][0] if cuts[k] < len(panels) else shape[0]
         want_end = panels[cuts[k + 1]][0] if cuts[k + 1] < len(panels) else shape[0]
         assert part.row_range == (want_begin, want_end), (k, part.row_range, want_begin, want_end)
+
+
+def test_tile_cache_round_trip(tmp_path):
+    """tsp_save / tsp_load: a handle restored from the cache file exports the same arrays and multiplies the same."""
+    import ctypes as C
+    from tilespmm_b200 import api, synth
+    rp, ci, v, shape = cases.banded_blocks(3001, 7000, 91)
+    for prec in (0, 1):
+        m = api.TileMatrix(prec).convert_host(shape, rp, ci, v, 2.0, 1.2, shard=(1, 2))
+        m.info()
+        path = str(tmp_path / f"tiles{prec}.bin").encode()
+        m.L.tsp_save.argtypes = [C.c_void_p, C.c_char_p]
+        m.L.tsp_load.argtypes = [C.c_void_p, C.c_char_p]
+        assert m.L.tsp_save(m.h, path) == 0, m.L.tsp_last_error()
+        r = api.TileMatrix(prec)
+        assert r.L.tsp_load(r.h, path) == 0, r.L.tsp_last_error()
+        r.shape = shape
+        assert r.info().tolist() == m.info().tolist() and r.row_range == m.row_range
+        for cls in range(3):
+            for w in _orc.ARRAYS:
+                np.testing.assert_array_equal(r.array(cls, w), m.array(cls, w))
+        B = api.to_values(synth.dense_b(shape[1], 64, 3), prec).reshape(shape[1], 64)
+        np.testing.assert_array_equal(r.spmm_host(B, 64), m.spmm_host(B, 64))
+        other = api.TileMatrix(1 - prec)
+        assert other.L.tsp_load(other.h, path) == 1 and b"holds" in other.L.tsp_last_error()
+        bad = tmp_path / "junk.bin"
+        bad.write_bytes(b"not a cache")
+        assert r.L.tsp_load(r.h, str(bad).encode()) == 1
