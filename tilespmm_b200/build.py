@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
             raise RuntimeError(f"nvcc failed on {src}")
     if procs or not os.path.exists(LIB) or force:
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcusparse", "-lcudart"]
+        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcusparse", "-lcudart", "-ldl"]
         subprocess.run(cmd, check=True)
     # the two drop-in executables (upstream bin/tilespmm_fp16, bin/tilespmm_tf32)
     os.makedirs(BIN, exist_ok=True)

@@ -2,6 +2,8 @@
 // runtime driver that mirrors upstream call_tilespmm_cuda (src/csr2tile.h:826-1093) and the cuSPARSE
 // baseline that mirrors upstream cusparse_spmm_all (src/main.cu:16-134).
 #include <cusparse.h>
+#include <dlfcn.h>
+#include <math.h>
 #include <stdarg.h>
 #include <stdlib.h>
 #include <string.h>
@@ -462,6 +464,60 @@ extern "C" int tsp_tune(tsp_handle *h, const void *d_b, float *d_c, int colB, in
     return check_device_error(h);
 }
 
+// SM clock in MHz through NVML (read only), or 0 when NVML is not available -- upstream get_gpu_clock (src/common.h:96-119)
+static unsigned int sm_clock_mhz(int device)
+{
+    typedef int (*InitFn)(void);
+    typedef int (*FindFn)(const char *, void **);
+    typedef int (*ClockFn)(void *, unsigned int, unsigned int *);
+    static void *dev[64];
+    static ClockFn clock_fn = nullptr;
+    static bool tried = false;
+    static FindFn find_fn = nullptr;
+    if (!tried)
+    {
+        tried = true;
+        void *lib = dlopen("libnvidia-ml.so.1", RTLD_LAZY);
+        InitFn init = lib ? (InitFn)dlsym(lib, "nvmlInit_v2") : nullptr;
+        find_fn = lib ? (FindFn)dlsym(lib, "nvmlDeviceGetHandleByPciBusId_v2") : nullptr;
+        clock_fn = lib ? (ClockFn)dlsym(lib, "nvmlDeviceGetClockInfo") : nullptr;
+        if (!init || !find_fn || !clock_fn || init() != 0) clock_fn = nullptr;
+    }
+    if (!clock_fn || device < 0 || device >= 64) return 0;
+    if (!dev[device])
+    {
+        char pci[32];
+        if (cudaDeviceGetPCIBusId(pci, sizeof(pci), device) != cudaSuccess || find_fn(pci, &dev[device]) != 0) { dev[device] = nullptr; return 0; }
+    }
+    unsigned int mhz = 0;
+    return clock_fn(dev[device], 1 /* NVML_CLOCK_SM */, &mhz) == 0 ? mhz : 0;
+}
+
+// Warm-up with clock stabilisation, upstream warmup_gpu (src/csr2tile.h:798-823): 20 passes, then batches of 50 until two
+// consecutive SM clock readings are at least 95% of the device clock rate and within 2% of each other; at most 1000
+// passes, or a fixed 100 when the clock cannot be read.
+static int warmup_like_upstream(tsp_handle *h, const void *d_b, float *d_c, int colB)
+{
+    int reference_khz = 0;
+    cudaDeviceGetAttribute(&reference_khz, cudaDevAttrClockRate, h->device);
+    const int limit = reference_khz > 0 && sm_clock_mhz(h->device) ? 1000 : 100;
+    unsigned int previous = 0;
+    for (int total = 0; total < limit;)
+    {
+        int count = total == 0 ? 20 : 50;
+        if (count > limit - total) count = limit - total;
+        for (int i = 0; i < count; i++) TSP_TRY(spmm_on(h, d_b, d_c, colB, 0));
+        TSP_CUDA(cudaStreamSynchronize(0));
+        total += count;
+        const unsigned int current = sm_clock_mhz(h->device);
+        if (reference_khz > 0 && previous && current && previous * 1000.0 >= reference_khz * 0.95 && current * 1000.0 >= reference_khz * 0.95 &&
+            fabsf((float)current / previous - 1.0f) <= 0.02f)
+            break;
+        previous = current;
+    }
+    return TSP_OK;
+}
+
 static double now_ms()
 {
     struct timeval t;
@@ -494,8 +550,7 @@ extern "C" int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB, int
     for (int k = 0; k < 3; k++) h->cls[k].TH = 0;
     if ((rc = ensure_schedules(h, colB)) != TSP_OK) return bail(rc);
     const double cand_ms = now_ms() - t_a;
-    for (int w = 0; w < 100; w++)  // warm-up; upstream polls the SM clock through NVML and falls back to 100 passes (src/csr2tile.h:798-823)
-        if ((rc = spmm_on(h, d_b, d_c, colB, 0)) != TSP_OK) return bail(rc);
+    if ((rc = warmup_like_upstream(h, d_b, d_c, colB)) != TSP_OK) return bail(rc);
     int best3[3];
     float tune_ms = 0.f;
     if ((rc = tsp_tune(h, d_b, d_c, colB, best3, &tune_ms)) != TSP_OK) return bail(rc);
@@ -506,8 +561,7 @@ extern "C" int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB, int
         tsp_set_error("run: copy of C failed");
         return bail(TSP_ECUDA);
     }
-    for (int w = 0; w < 100; w++)
-        if ((rc = spmm_on(h, d_b, d_c, colB, 0)) != TSP_OK) return bail(rc);
+    if ((rc = warmup_like_upstream(h, d_b, d_c, colB)) != TSP_OK) return bail(rc);
     float ms = 0.f;
     if ((rc = tsp_time(h, -1, d_b, d_c, colB, repeat, &ms)) != TSP_OK) return bail(rc);
     out6[0] = best3[0]; out6[1] = best3[1]; out6[2] = best3[2];
