@@ -408,7 +408,7 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (key: workload, class); None where no capture exists.
-TRAFFIC = {("c2", 2): 346.9e6, ("c2", 1): 419.8e6, ("c2", 0): 854.8e6}   # profiles/c2_spmm_{8,16,64}row_*.md
+TRAFFIC = {("c2", 2): 347.1e6, ("c2", 1): 420.1e6, ("c2", 0): 853.2e6}   # profiles/c2_spmm_{8,16,64}row_*.md
 
 if __name__ == "__main__":
     main()
