@@ -92,3 +92,17 @@ def test_fullsize_shards_concatenate():
         p.close()
     torch.cuda.synchronize()
     assert torch.equal(torch.cat(parts), Cf[:shape[0]])
+
+
+def test_fullsize_with_the_transposed_tcgen05_kernels():
+    """Same properties with the tcgen05 kernel of the 16/8-row classes (TSP_SMALL=t, chosen once per process): R-MAT and
+    the mixed-density matrix have long and split panels, which is where its two MMA issuers and out-of-order slot
+    releases are exercised."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, TSP_SMALL="t")
+    here = os.path.abspath(__file__)
+    r = subprocess.run([sys.executable, "-m", "pytest", here, "-x", "-q", "-m", "gpu", "-k", "rowsums_linearity or shards_concatenate"],
+                       env=env, capture_output=True, text=True, timeout=1800)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

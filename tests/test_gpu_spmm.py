@@ -168,3 +168,17 @@ def test_tma_gather4_variant_of_the_64_row_kernel():
     r = subprocess.run([sys.executable, "-m", "pytest", here, "-x", "-q", "-m", "gpu", "-k",
                         "(gd0 or exact or split) and not tma_gather4 and not async"], env=env, capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+def test_transposed_tcgen05_variant_of_the_small_kernels():
+    """The 16/8-row classes have a second kernel: persistent, tcgen05.mma on the transposed product with the accumulators
+    in tensor memory (TSP_SMALL=t, chosen once per process; widths that are multiples of 64).  Run the parity cases of
+    this file in a child process with that variant."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, TSP_SMALL="t")
+    here = os.path.abspath(__file__)
+    r = subprocess.run([sys.executable, "-m", "pytest", here, "-x", "-q", "-m", "gpu", "-k",
+                        "not tma_gather4 and not transposed_tcgen05 and not async"], env=env, capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

