@@ -189,6 +189,7 @@ def main():
     ap.add_argument("--delta", type=float, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cusparse", action="store_true")
+    ap.add_argument("--no-gather-probe", action="store_true", help="skip the L2 gather ceiling measurement")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--th", default=None, help="th64,th16,th8: fixed thresholds, skips the on-GPU tuning (profiling runs)")
     args = ap.parse_args()
@@ -337,6 +338,15 @@ def main():
             # why the algorithmic fraction above exceeds 1
             roofline["dram_gbs"] = roofline["traffic"] / (cls_ms[dom] * 1e-3) / 1e9
             roofline["dram_frac"] = roofline["dram_gbs"] / peak
+        if rank == 0 and dom != 0 and not args.no_gather_probe:
+            # the ceiling that does bind the 16/8-row kernels: gathering row segments of this width out of an L2-side
+            # buffer of B's size, measured live with a bare gather loop (tsp_probe_gather)
+            vsz = 2 if prec == 0 else 4
+            seg = min(512, cb * vsz)   # one task unit gathers stripes of up to 128 columns
+            if seg in (128, 256, 512):
+                ceil = api.probe_gather(seg, int(shape[1]) * cb * vsz, local)
+                gath = float(b3[1]) / (cls_ms[dom] * 1e-3) / 1e9
+                roofline["gather"] = {"segment_bytes": seg, "achieved_gbs": gath, "probe_gbs": ceil, "frac": gath / ceil}
     all_bytes = float(m.algorithmic_bytes(cb).sum())
 
     # end to end through the C ABI with host buffers: H2D of B, kernels, D2H of C inside the timed region

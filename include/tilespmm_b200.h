@@ -154,6 +154,12 @@ int tsp_read_mtx(const char *path, int *m, int *n, long long *nnz, int *is_symme
                  float **h_val);
 void tsp_free_host(void *p);
 
+/* ---- measurement aid (no upstream counterpart): the rate, in GB/s, at which all SMs of the device together gather
+ * randomly chosen row segments of row_bytes (128, 256 or 512) from a zero-filled buffer of buffer_bytes with plain
+ * 16-byte loads.  With a buffer of the size of the dense operand B this is the ceiling of the gather in the SpMM
+ * kernels, which read every gathered row from L2. */
+int tsp_probe_gather(int device, int row_bytes, long long buffer_bytes, double *gb_per_s);
+
 #ifdef __cplusplus
 }
 #endif

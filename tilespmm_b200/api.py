@@ -53,6 +53,7 @@ def lib() -> C.CDLL:
         L.tsp_algorithmic_bytes.argtypes = [vp, i, i, vp]
         L.tsp_time.argtypes = [vp, i, vp, vp, i, i, C.POINTER(f)]
         L.tsp_run.argtypes = [vp, vp, vp, i, i, C.c_double, i, vp]
+        L.tsp_probe_gather.argtypes = [i, i, ll, C.POINTER(C.c_double)]
         L.tsp_cusparse_baseline.argtypes = [i, i, i, i, ll, vp, vp, vp, i, i, vp, vp, i, i, vp]
         L.tsp_features_from_csr.argtypes = [i, i, ll, vp, C.c_double, i, vp]
         L.tilespmm_predict_fp16.argtypes = [vp, C.POINTER(f), C.POINTER(f)]
@@ -95,6 +96,14 @@ def features_from_csr(rowptr, shape, capability: float, colB: int) -> np.ndarray
     if not lib().tsp_features_from_csr(shape[0], shape[1], int(rowptr[-1]), _p(rowptr), capability, colB, _p(f)):
         raise TileSpMMError("inconsistent CSR row pointer")
     return f
+
+
+def probe_gather(row_bytes: int, buffer_bytes: int, device: int = 0) -> float:
+    """GB/s at which the device gathers random row segments of row_bytes out of a buffer of buffer_bytes (the
+    L2 side ceiling of the SpMM kernels' gather)."""
+    out = C.c_double(0)
+    _check(lib().tsp_probe_gather(device, row_bytes, buffer_bytes, C.byref(out)), "tsp_probe_gather")
+    return out.value
 
 
 def predict(precision: int, features) -> tuple[float, float]:

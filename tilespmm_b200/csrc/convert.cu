@@ -421,7 +421,7 @@ void tsp_free_tiles(tsp_handle *h)
     {
         TspClass &c = h->cls[k];
         cudaFree(c.d_tile_ptr); cudaFree(c.d_tile_nnz); cudaFree(c.d_tile_colidx); cudaFree(c.d_panel_row); cudaFree(c.d_val);
-        cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_split_row); cudaFree(c.d_task_count);
+        cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_split_row); cudaFree(c.d_task_count); cudaFree(c.d_task_pack);
         c = TspClass();
         c.BM = tsp_bm(k);
         c.BN = tsp_bn(h->precision, k);

@@ -6,6 +6,7 @@
 // of tiles per panel, in float and in upstream's evaluation order, with the resource rows of THESE kernels.
 #include <cub/cub.cuh>
 #include <math.h>
+#include <stdlib.h>
 
 #include "tsp_internal.cuh"
 
@@ -53,6 +54,63 @@ __global__ void k_task_fill(int tilem, const int *__restrict__ tile_ptr, const i
     split_row[atomicAdd(split_count, 1)] = row;
 }
 
+// sort key of a task: longer tasks get smaller keys
+__global__ void k_task_keys(int ntasks, const int *__restrict__ task_start, unsigned int *__restrict__ keys, int *__restrict__ ids)
+{
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= ntasks) return;
+    const int len = task_start[t + 1] - task_start[t];
+    keys[t] = 0xffffu - (unsigned int)(len > 0xffff ? 0xffff : len);
+    ids[t] = t;
+}
+
+__global__ void k_task_pack(int ntasks, const int *__restrict__ order, const unsigned int *__restrict__ task_row,
+                            const int *__restrict__ task_start, uint4 *__restrict__ pack)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ntasks) return;
+    const int t = order ? order[i] : i;
+    pack[i] = make_uint4(task_row[t], (unsigned int)task_start[t], (unsigned int)task_start[t + 1], 0u);
+}
+
+// The 16/8-row kernels run four tasks per CTA, one per warp, and a CTA holds its SM resources until its longest
+// task is done.  Walking the tasks longest first (stable, so equal tasks keep their panel order and with it the
+// locality of their B rows in L2) puts tasks of similar length into one CTA and the long ones at the front of the
+// launch.  TSP_TASK_ORDER=0 in the environment keeps panel order.
+int build_task_pack(TspClass &c)
+{
+    if (c.ntasks == 0) return TSP_OK;
+    static int sorted = -1;
+    if (sorted < 0) { const char *e = getenv("TSP_TASK_ORDER"); sorted = (e && e[0] == '0') ? 0 : 1; }
+    const int T = 256, n = c.ntasks;
+    unsigned int *keys = nullptr, *keys_out = nullptr;
+    int *ids = nullptr, *ids_out = nullptr;
+    void *scratch = nullptr;
+    cudaError_t e = cudaSuccess;
+    if (sorted)
+    {
+        size_t bytes = 0;
+        e = cudaMalloc((void **)&keys, (size_t)n * 16);   // keys, sorted keys, ids, sorted ids
+        if (e == cudaSuccess)
+        {
+            keys_out = keys + n; ids = (int *)(keys + 2 * (size_t)n); ids_out = ids + n;
+            k_task_keys<<<(n + T - 1) / T, T>>>(n, c.d_task_start, keys, ids);
+            e = cub::DeviceRadixSort::SortPairs(nullptr, bytes, keys, keys_out, ids, ids_out, n, 0, 16);
+        }
+        if (e == cudaSuccess) e = cudaMalloc(&scratch, bytes ? bytes : 1);
+        if (e == cudaSuccess) e = cub::DeviceRadixSort::SortPairs(scratch, bytes, keys, keys_out, ids, ids_out, n, 0, 16);
+    }
+    if (e == cudaSuccess)
+    {
+        k_task_pack<<<(n + T - 1) / T, T>>>(n, sorted ? ids_out : nullptr, c.d_task_row, c.d_task_start, c.d_task_pack);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();   // the scratch goes away below
+    cudaFree(scratch); cudaFree(keys);
+    TSP_CUDA(e);
+    return TSP_OK;
+}
+
 }  // namespace
 
 int tsp_schedule(tsp_handle *h, int cls, int TH)
@@ -82,11 +140,12 @@ int tsp_schedule(tsp_handle *h, int cls, int TH)
     TSP_CUDA(e);
     if ((long long)ntasks > c.cap_tasks)
     {
-        cudaFree(c.d_task_row); cudaFree(c.d_task_start);
-        c.d_task_row = nullptr; c.d_task_start = nullptr;
+        cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_task_pack);
+        c.d_task_row = nullptr; c.d_task_start = nullptr; c.d_task_pack = nullptr;
         c.cap_tasks = (long long)ntasks + ntasks / 4 + 16;
         TSP_CUDA(cudaMalloc((void **)&c.d_task_row, (size_t)c.cap_tasks * 4));
         TSP_CUDA(cudaMalloc((void **)&c.d_task_start, ((size_t)c.cap_tasks + 1) * 4));
+        if (cls != 0) TSP_CUDA(cudaMalloc((void **)&c.d_task_pack, (size_t)c.cap_tasks * sizeof(uint4)));
     }
     int *d_split_count = c.d_task_count + c.tilem + 1;
     TSP_CUDA(cudaMemset(d_split_count, 0, 4));
@@ -95,6 +154,7 @@ int tsp_schedule(tsp_handle *h, int cls, int TH)
     TSP_CUDA(cudaGetLastError());
     TSP_CUDA(cudaMemcpy(&c.nsplit, d_split_count, 4, cudaMemcpyDeviceToHost));
     c.ntasks = ntasks;
+    if (cls != 0) TSP_TRY(build_task_pack(c));
     return TSP_OK;
 }
 

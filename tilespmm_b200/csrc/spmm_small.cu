@@ -121,8 +121,8 @@ __device__ __forceinline__ int swz(int c, int k)
 
 template <int PREC, int CLS, int NS>
 __global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? 6 : 4))
-k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const unsigned int *__restrict__ task_row,
-             const int *__restrict__ task_start, const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
+k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const uint4 *__restrict__ task_pack,
+             const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
              const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err)
 {
     using Cfg = SmallCfg<PREC, CLS, NS>;
@@ -134,10 +134,11 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     const int task = (int)(unit / nstripes), stripe = (int)(unit - (long long)task * nstripes);
     unsigned char *ring = smem_raw + warp * Cfg::WARP_BYTES;
 
-    const unsigned int trow = task_row[task];
+    const uint4 tp = __ldg(task_pack + task);   // {row word, first tile, end tile, -}: one load per task
+    const unsigned int trow = tp.x;
     const bool split = (trow >> 31) != 0;
     const int first_row = (int)(trow & 0x7fffffffu) - row_begin;
-    const int t0 = task_start[task], nt = task_start[task + 1] - t0;
+    const int t0 = (int)tp.y, nt = (int)tp.z - t0;
     const size_t stripe_bytes = (size_t)stripe * NS * SZ;
     const size_t ldb_bytes = (size_t)ldb * SZ;
 
@@ -400,7 +401,7 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
     const long long units = (long long)c.ntasks * nstripes;
     const int grid = (int)((units + WARPS - 1) / WARPS);
     if (grid == 0) return TSP_OK;
-    kern<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_row, c.d_task_start, c.d_tile_colidx,
+    kern<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_pack, c.d_tile_colidx,
                                             (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error);
     TSP_CUDA(cudaGetLastError());
     h->launches++;

@@ -106,6 +106,8 @@ struct TspClass
     long long cap_tasks = 0;
     unsigned int *d_task_row = nullptr;
     int *d_task_start = nullptr, *d_split_row = nullptr, *d_task_count = nullptr;
+    // the same tasks as {row word, first tile, end tile, 0}, longest first (what the 16/8-row kernels walk)
+    uint4 *d_task_pack = nullptr;
 };
 
 struct tsp_handle
