@@ -16,10 +16,10 @@ namespace
 {
 
 constexpr int WARPS = 4;
-// Ring depth per warp.  Occupancy beats depth on B200 (24 resident warps with 2 stages outrun 12 warps with 4),
-// so the ring only grows while a warp's ring stays within ~9 KB: 2 stages for 128-column stripes, 4 for 64, 6 for 32
-// (narrow stripes also mean small grids, where the per-warp chain of tile latencies is what is left to hide).
-constexpr int ring_stages(int stage_bytes) { return 9216 / stage_bytes < 2 ? 2 : (9216 / stage_bytes > 6 ? 6 : 9216 / stage_bytes); }
+// Ring depth per warp.  Occupancy beats depth on B200: on the stencil 24 resident warps with 2 stages outrun 12 warps
+// with 4 (0.130 vs 0.165 ms), on R-MAT (64-column stripes, FP16) 2 stages at 8 CTAs per SM outrun 4 stages at 6
+// (0.347 vs 0.402 ms).  So: 2 stages for 128- and 64-column stripes, 3 for 32-column ones.
+constexpr int ring_stages(int stage_bytes) { return 4608 / stage_bytes < 2 ? 2 : 4608 / stage_bytes; }
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
 {
@@ -120,7 +120,7 @@ __device__ __forceinline__ int swz(int c, int k)
 }
 
 template <int PREC, int CLS, int NS>
-__global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? 6 : 4))
+__global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const uint4 *__restrict__ task_pack,
              const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
              const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err)
