@@ -418,7 +418,8 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (key: workload, class); None where no capture exists.
-TRAFFIC = {("c2", 2): 347.1e6, ("c2", 1): 420.1e6, ("c2", 0): 853.2e6}   # profiles/c2_spmm_{8,16,64}row_*.md
+# ncu DRAM bytes (read + write) of one launch of the class kernel: profiles/c2_spmm_{8,16,64}row_*.md, profiles/c3_spmm_8row_fp16.md
+TRAFFIC = {("c2", 2): 372.9e6, ("c2", 1): 443.3e6, ("c2", 0): 853.2e6, ("c3", 2): 1123.4e6}
 
 if __name__ == "__main__":
     main()
