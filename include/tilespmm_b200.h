@@ -141,6 +141,13 @@ int tsp_cusparse_baseline(int device, int precision, int m, int k, long long nnz
                           const int *h_colidx, const void *h_val, int n, int ldb, const void *h_b, float *h_c,
                           int warmup, int repeat, double *out3);
 
+/* The same measurement with another cuSPARSE algorithm: alg 0 = ALG_DEFAULT (what upstream runs), 1..3 =
+ * CUSPARSE_SPMM_CSR_ALG1..3, with cusparseSpMM_preprocess counted in pre_time_ms.  A stronger baseline, reported
+ * beside upstream's number, never instead of it. */
+int tsp_cusparse_baseline_alg(int device, int precision, int m, int k, long long nnz, const int *h_rowptr,
+                              const int *h_colidx, const void *h_val, int n, int ldb, const void *h_b, float *h_c,
+                              int warmup, int repeat, int alg, double *out3);
+
 /* ---- tile cache on disk (no upstream counterpart: upstream converts on every run).  tsp_save writes the converted
  * matrix of the handle (all classes, shard limits included) to one binary file; tsp_load restores it into a handle of
  * the same precision, replacing whatever it held, without touching the CSR again. */

@@ -182,3 +182,23 @@ def test_transposed_tcgen05_variant_of_the_small_kernels():
     r = subprocess.run([sys.executable, "-m", "pytest", here, "-x", "-q", "-m", "gpu", "-k",
                         "not tma_gather4 and not transposed_tcgen05 and not async"], env=env, capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+
+
+def test_cusparse_algorithms_and_gather_probe():
+    """The stronger cuSPARSE baselines (CSR_ALG1..3) give the same product as upstream's ALG_DEFAULT, and the gather
+    probe answers with a plausible rate."""
+    import numpy as np
+    from tilespmm_b200 import api, synth
+    rp, ci, v, shape = synth.fixed_nnz_per_row(2048, 12, seed=11)
+    vi = np.round(v * 4).astype(np.float32)
+    B = np.round(synth.dense_b(shape[1], 64, 3, "uniform") * 4).astype(np.float32)
+    for prec in (0, 1):
+        Bv = api.to_values(B, prec).reshape(shape[1], 64)
+        ref = None
+        for alg in (0, 1, 2, 3):
+            out3, c = api.cusparse_baseline(prec, shape, rp, ci, vi, Bv, 64, warmup=1, repeat=2, alg=alg)
+            assert out3[1] > 0 and out3[2] > 0
+            ref = c if ref is None else ref
+            np.testing.assert_array_equal(c, ref)     # small integers: exact in every algorithm
+    gbs = api.probe_gather(512, 64 << 20)
+    assert 1000.0 < gbs < 40000.0

@@ -228,13 +228,18 @@ class TileMatrix:
         return out6, c
 
 
-def cusparse_baseline(precision, shape, rowptr, colidx, vals, h_b, colB, device=0, warmup=100, repeat=1000, want_c=True):
-    """The cuSPARSE CSR SpMM upstream runs beside its own kernels (src/main.cu:16-134)."""
+def cusparse_baseline(precision, shape, rowptr, colidx, vals, h_b, colB, device=0, warmup=100, repeat=1000, want_c=True, alg=0):
+    """The cuSPARSE CSR SpMM upstream runs beside its own kernels (src/main.cu:16-134); alg 1..3 select
+    CUSPARSE_SPMM_CSR_ALG1..3 instead of upstream's ALG_DEFAULT."""
     rowptr = np.ascontiguousarray(rowptr, np.int32)
     colidx = np.ascontiguousarray(colidx, np.int32)
     v = vals if (isinstance(vals, np.ndarray) and vals.dtype == np.uint16) else to_values(vals, precision)
     out3 = np.zeros(3, dtype=np.float64)
     c = np.zeros((shape[0], colB), dtype=np.float32) if want_c else None
-    _check(lib().tsp_cusparse_baseline(device, precision, shape[0], shape[1], colidx.size, _p(rowptr), _p(colidx), _p(v),
-                                       colB, h_b.shape[1], _p(h_b), _p(c), warmup, repeat, _p(out3)), "tsp_cusparse_baseline")
+    if alg:
+        _check(lib().tsp_cusparse_baseline_alg(device, precision, shape[0], shape[1], colidx.size, _p(rowptr), _p(colidx), _p(v),
+                                               colB, h_b.shape[1], _p(h_b), _p(c), warmup, repeat, alg, _p(out3)), "tsp_cusparse_baseline_alg")
+    else:
+        _check(lib().tsp_cusparse_baseline(device, precision, shape[0], shape[1], colidx.size, _p(rowptr), _p(colidx), _p(v),
+                                           colB, h_b.shape[1], _p(h_b), _p(c), warmup, repeat, _p(out3)), "tsp_cusparse_baseline")
     return out3, c

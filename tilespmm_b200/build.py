@@ -24,7 +24,8 @@ def _newer(target: str, deps: list[str]) -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compiles every translation unit to an object and links the shared library.  Returns its path."""
     nvcc = os.environ.get("NVCC", "nvcc")
-    headers = [os.path.join(CSRC, "tsp_internal.cuh"), os.path.join(HERE, "..", "include", "tilespmm_b200.h")]
+    headers = [os.path.join(CSRC, "tsp_internal.cuh"), os.path.join(HERE, "..", "include", "tilespmm_b200.h"),
+               os.path.join(CSRC, "model_table.inc")]
     objs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     procs = []

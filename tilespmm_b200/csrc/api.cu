@@ -578,10 +578,27 @@ extern "C" int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB, int
 }
 
 // upstream cusparse_spmm_all (src/main.cu:16-134)
+static int cusparse_baseline(int device, int precision, int m, int k, long long nnz, const int *rp, const int *ci, const void *val,
+                             int n, int ldb, const void *h_b, float *h_c, int warmup, int repeat, int alg_id, double *out3);
+
 extern "C" int tsp_cusparse_baseline(int device, int precision, int m, int k, long long nnz, const int *rp, const int *ci, const void *val,
                                      int n, int ldb, const void *h_b, float *h_c, int warmup, int repeat, double *out3)
 {
+    return cusparse_baseline(device, precision, m, k, nnz, rp, ci, val, n, ldb, h_b, h_c, warmup, repeat, 0, out3);
+}
+
+extern "C" int tsp_cusparse_baseline_alg(int device, int precision, int m, int k, long long nnz, const int *rp, const int *ci, const void *val,
+                                         int n, int ldb, const void *h_b, float *h_c, int warmup, int repeat, int alg, double *out3)
+{
+    if (alg < 0 || alg > 3) { tsp_set_error("cusparse_baseline_alg: alg must be 0 (default), 1, 2 or 3 (CSR_ALG1..3)"); return TSP_EINVAL; }
+    return cusparse_baseline(device, precision, m, k, nnz, rp, ci, val, n, ldb, h_b, h_c, warmup, repeat, alg, out3);
+}
+
+static int cusparse_baseline(int device, int precision, int m, int k, long long nnz, const int *rp, const int *ci, const void *val,
+                             int n, int ldb, const void *h_b, float *h_c, int warmup, int repeat, int alg_id, double *out3)
+{
     if (!rp || !ci || !val || !h_b || !out3 || repeat <= 0) { tsp_set_error("cusparse_baseline: bad argument"); return TSP_EINVAL; }
+    const cusparseSpMMAlg_t alg = alg_id == 1 ? CUSPARSE_SPMM_CSR_ALG1 : alg_id == 2 ? CUSPARSE_SPMM_CSR_ALG2 : alg_id == 3 ? CUSPARSE_SPMM_CSR_ALG3 : CUSPARSE_SPMM_ALG_DEFAULT;
     TSP_CUDA(cudaSetDevice(device));
     const size_t vsz = precision ? 4 : 2;
     int *d_rp = nullptr, *d_ci = nullptr;
@@ -609,19 +626,23 @@ extern "C" int tsp_cusparse_baseline(int device, int precision, int m, int k, lo
         const float alpha = 1.0f, beta = 0.0f;
         size_t bytes = 0;
         if (cusparseSpMM_bufferSize(handle, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A, B, &beta, Cm, CUDA_R_32F,
-                                    CUSPARSE_SPMM_ALG_DEFAULT, &bytes)) { fail("cusparseSpMM_bufferSize"); break; }
+                                    alg, &bytes)) { fail("cusparseSpMM_bufferSize"); break; }
         if (cudaMalloc(&buf, bytes ? bytes : 1)) { fail("cudaMalloc buffer"); break; }
+        // the non-default algorithms may analyse the matrix once; that time goes into pre_time like every other set-up step
+        if (alg_id != 0 && cusparseSpMM_preprocess(handle, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A, B, &beta, Cm,
+                                                   CUDA_R_32F, alg, buf)) { fail("cusparseSpMM_preprocess"); break; }
+        if (cudaDeviceSynchronize()) { fail("cusparseSpMM_preprocess"); break; }
         out3[0] = now_ms() - t_a;
         bool bad = false;
         for (int i = 0; i < warmup && !bad; i++)
             bad = cusparseSpMM(handle, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A, B, &beta, Cm, CUDA_R_32F,
-                               CUSPARSE_SPMM_ALG_DEFAULT, buf) != CUSPARSE_STATUS_SUCCESS;
+                               alg, buf) != CUSPARSE_STATUS_SUCCESS;
         if (bad || cudaDeviceSynchronize()) { fail("cusparseSpMM warm-up"); break; }
         cudaEventCreate(&t0); cudaEventCreate(&t1);
         cudaEventRecord(t0, cudaStreamLegacy);
         for (int i = 0; i < repeat && !bad; i++)
             bad = cusparseSpMM(handle, CUSPARSE_OPERATION_NON_TRANSPOSE, CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, A, B, &beta, Cm, CUDA_R_32F,
-                               CUSPARSE_SPMM_ALG_DEFAULT, buf) != CUSPARSE_STATUS_SUCCESS;
+                               alg, buf) != CUSPARSE_STATUS_SUCCESS;
         cudaEventRecord(t1, cudaStreamLegacy);
         if (bad || cudaEventSynchronize(t1)) { fail("cusparseSpMM"); break; }
         float ms = 0.f;

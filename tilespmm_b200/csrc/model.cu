@@ -1,7 +1,9 @@
 // Threshold model: (gamma, delta) from 11 matrix / device features.  Same C ABI as upstream lib/model.so
 // (src/ml_predict.h:8-15, src/ml_predict.c:9-17); the answer is always one of upstream's 66 candidate pairs
-// (src/model.h:14-38).  Upstream's decision table was fitted to its own kernels on other GPUs and is not
-// reproduced here; the rules below were derived from sweeps of the candidate pairs with THESE kernels on a B200.
+// (src/model.h:14-38), found by walking a decision table in upstream's node format (src/model.h:9-13, walk at
+// 3463-3491).  Upstream's own table was fitted to its kernels on other GPUs and is not reproduced here: the table in
+// model_table.inc comes from `python -m tilespmm_b200.retrain_model` (sweep of all candidates on a seeded corpus with
+// THESE kernels on a B200, then a small tree that minimises the summed regret).
 #include <math.h>
 
 #include "../../include/tilespmm_b200.h"
@@ -9,23 +11,59 @@
 namespace
 {
 
-const float kGammaGrid[10] = {1.0f, 1.39999998f, 1.79999995f, 2.0f, 2.4000001f, 2.79999995f, 3.0f, 3.4000001f, 3.79999995f, 4.0f};
-const float kDeltaGrid[6] = {1.0f, 1.20000005f, 1.39999998f, 1.5f, 1.79999995f, 2.0f};
+// the candidate pairs in upstream's order: three fixed shortcuts, the 10 x 6 grid, three extras
+const float kCandidates[66][2] = {
+    {0.0f, 1.5f}, {5.0f, 0.0f}, {5.0f, 3.0f},
+#define TSP_ROW(g) {g, 1.0f}, {g, 1.20000005f}, {g, 1.39999998f}, {g, 1.5f}, {g, 1.79999995f}, {g, 2.0f}
+    TSP_ROW(1.0f), TSP_ROW(1.39999998f), TSP_ROW(1.79999995f), TSP_ROW(2.0f), TSP_ROW(2.4000001f),
+    TSP_ROW(2.79999995f), TSP_ROW(3.0f), TSP_ROW(3.4000001f), TSP_ROW(3.79999995f), TSP_ROW(4.0f),
+#undef TSP_ROW
+    {2.5f, 1.0f}, {2.5f, 1.20000005f}, {3.5f, 1.0f}};
 
-void pick(int precision, const double *f, float *gamma, float *delta)
+struct TspPolicyNode
 {
-    // Sweeps of the candidate pairs on B200 (4096^2 fixed-degree, 27-point stencil, R-MAT scale 20, mixed dense
-    // blocks; FP16 and TF32; widths 32-256): 8-row tiles win wherever the 64-row window does not reuse almost
-    // every column, and 16-row tiles never beat them with these kernels.  gamma = 3.8 admits 64-row panels only
-    // when the four 16-row sub-windows together hold more than 3.8x the distinct columns of the 64-row window
-    // (dense blocks); delta = 2.0 sends everything else to 8-row tiles.  The features do not change the answer
-    // for now; the signature keeps them so that a fitted table can replace this rule.
-    (void)precision; (void)f;
-    *gamma = kGammaGrid[8];
-    *delta = kDeltaGrid[5];
+    int feature, left_feature, right_feature;
+    int child0, child1, child2, child3, missing_left_mask;
+    float cut, left_cut, right_cut;
+};
+
+#include "model_table.inc"
+
+void pick(int root, const double *f, float *gamma, float *delta)
+{
+    int index = root;
+    const int nnodes = (int)(sizeof(kPolicyNodes) / sizeof(kPolicyNodes[0]));
+    for (int steps = 0; index >= 0 && index < nnodes && steps < nnodes + 1; steps++)   // a well-formed table never loops
+    {
+        const TspPolicyNode &n = kPolicyNodes[index];
+        float v = (float)f[n.feature + 2];
+        const bool left = isnan(v) ? (n.missing_left_mask & 1) != 0 : v < n.cut;
+        if (left)
+        {
+            if (n.left_feature < 0) index = n.child0;
+            else
+            {
+                v = (float)f[n.left_feature + 2];
+                index = (isnan(v) ? (n.missing_left_mask & 2) != 0 : v < n.left_cut) ? n.child0 : n.child1;
+            }
+        }
+        else
+        {
+            if (n.right_feature < 0) index = n.child2;
+            else
+            {
+                v = (float)f[n.right_feature + 2];
+                index = (isnan(v) ? (n.missing_left_mask & 4) != 0 : v < n.right_cut) ? n.child2 : n.child3;
+            }
+        }
+    }
+    int action = -1 - index;
+    if (action < 0 || action >= 66) action = 3 + 8 * 6 + 5;   // malformed table: the single-rule answer (3.8, 2.0)
+    *gamma = kCandidates[action][0];
+    *delta = kCandidates[action][1];
 }
 
 }  // namespace
 
-extern "C" void tilespmm_predict_fp16(const double *features, float *gamma, float *delta) { pick(0, features, gamma, delta); }
-extern "C" void tilespmm_predict_tf32(const double *features, float *gamma, float *delta) { pick(1, features, gamma, delta); }
+extern "C" void tilespmm_predict_fp16(const double *features, float *gamma, float *delta) { pick(kPolicyRootFp16, features, gamma, delta); }
+extern "C" void tilespmm_predict_tf32(const double *features, float *gamma, float *delta) { pick(kPolicyRootTf32, features, gamma, delta); }
