@@ -90,9 +90,6 @@ __device__ __forceinline__ void cp_async4(unsigned smem, const void *gmem)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem), "l"(gmem));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int K>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(K) : "memory"); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count)); }
 // arrive on the mbarrier when every cp.async this thread has issued so far has landed; the thread itself does not wait
 __device__ __forceinline__ void cp_async_arrive(unsigned bar)
@@ -176,8 +173,8 @@ __device__ __forceinline__ Unit load_unit(long long u, long long nunits, int nst
     return r;
 }
 
-// group descriptor, second word: tiles | first group of its unit | last group of its unit | stripe | end of stream
-constexpr unsigned D_FIRST = 1u << 4, D_LAST = 1u << 5, D_END = 1u << 31;
+// group descriptor: {first tile, tiles (bits 0-3) | stripe (bits 8-23) | end of stream (bit 31)}
+constexpr unsigned D_END = 1u << 31;
 
 template <int PREC, int CLS, int NS>
 __global__ void __launch_bounds__(THREADS, CTAS)
@@ -240,7 +237,6 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
         Unit cur = load_unit(u, nunits, nstripes, task_start);
         Unit nxt = load_unit(u + stride, nunits, nstripes, task_start);
         int x = 0;
-        bool first = true;   // the next group opens a unit
         int ends_sent = 0;   // every producer warp takes every PW-th group, so each gets its own end marker
         while (ends_sent < PW && ok)
         {
@@ -248,7 +244,7 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
             while (u < nunits && cur.t0 == cur.t1)
             {
                 // empty from the start or used up (t0 advances through the unit)
-                u += stride; cur = nxt; first = true;
+                u += stride; cur = nxt;
                 nxt = load_unit(u + stride, nunits, nstripes, task_start);
             }
             const bool end = u >= nunits;
@@ -266,8 +262,7 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
                 const int left = cur.t1 - cur.t0;
                 const int cnt = left < G ? left : G;
                 if (lane == 0)
-                    desc_ring[slot] = make_uint2((unsigned)cur.t0, (unsigned)cnt | (first ? D_FIRST : 0u) | (left <= G ? D_LAST : 0u) | ((unsigned)cur.stripe << 8));
-                first = false;
+                    desc_ring[slot] = make_uint2((unsigned)cur.t0, (unsigned)cnt | ((unsigned)cur.stripe << 8));
                 if (lane * 4 < cnt * C::BN)
                     cp_async16(smem_u32(&idx_ring[slot][lane * 4]), tile_colidx + (size_t)cur.t0 * C::BN + lane * 4);
                 cur.t0 += cnt;
@@ -299,7 +294,6 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
         }
         // values: lane l of the fragment-order tile owns words l*AW .. l*AW + AW-1; word j goes to row j, word l
         const unsigned char *gbase = dB + (size_t)c_mine * 16;
-        int ngroups = 0;
         for (int gi = warp; ok; gi += PW)
         {
             const int slot = gi % R;
@@ -342,7 +336,6 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
             // the slot's full barrier takes one arrival per lane, delivered when that lane's copies have landed: nobody
             // waits for data here, so every slot the MMA has released is in flight
             cp_async_arrive(bar_full + 8 * s);
-            ngroups++;
         }
         asm volatile("cp.async.wait_all;\n" ::: "memory");
     }
