@@ -1,7 +1,7 @@
 """Side-by-side measurement on one GPU box: this library vs the UNMODIFIED upstream kernels (oracle/_ref, built for
 sm_100a) vs cuSPARSE, on the benchmark configurations, with C parity between all of them.
 
-    python tests/compare_upstream_gpu.py [c1 c2 c3 c4] [--scale S] > gpurun_out/compare.jsonl
+    python tests/compare_upstream_gpu.py [c1 c2 c3 c4] [--scale S] > compare.jsonl
 
 Not a pytest file (it lives here because only tests may drive oracle/).  One JSON line per configuration.
 Upstream is driven through its own call_tilespmm_cuda (thresholds from its own model at capability 10.0, its own
