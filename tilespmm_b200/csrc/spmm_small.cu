@@ -119,7 +119,10 @@ __device__ __forceinline__ int swz(int c, int k)
     return c ^ ((k >> 1) & 3);
 }
 
-template <int PREC, int CLS, int NS>
+// COOP: the four warps of a CTA share ONE (task, stripe): warp w takes tiles w, w+4, ... and the partial blocks are
+// added up through shared memory.  Used for launches that would not fill the GPU with one warp per unit: the chain of
+// dependent tile fetches of a panel is four times shorter.
+template <int PREC, int CLS, int NS, bool COOP>
 __global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const uint4 *__restrict__ task_pack,
              const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
@@ -129,8 +132,8 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES, RBS = Cfg::RBS;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long unit = (long long)blockIdx.x * WARPS + warp;
-    if (unit >= (long long)ntasks * nstripes) return;
+    const long long unit = COOP ? (long long)blockIdx.x : (long long)blockIdx.x * WARPS + warp;
+    if (unit >= (long long)ntasks * nstripes) return;   // COOP: never (one CTA per unit)
     const int task = (int)(unit / nstripes), stripe = (int)(unit - (long long)task * nstripes);
     unsigned char *ring = smem_raw + warp * Cfg::WARP_BYTES;
 
@@ -138,7 +141,10 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     const unsigned int trow = tp.x;
     const bool split = (trow >> 31) != 0;
     const int first_row = (int)(trow & 0x7fffffffu) - row_begin;
-    const int t0 = (int)tp.y, nt = (int)tp.z - t0;
+    // tiles of this warp: t0, t0 + TS, ... (TS = 1: all tiles of the task)
+    constexpr int TS = COOP ? WARPS : 1;
+    const int t0 = (int)tp.y + (COOP ? warp : 0);
+    const int nt = (int)tp.z > t0 ? ((int)tp.z - t0 + TS - 1) / TS : 0;
     const size_t stripe_bytes = (size_t)stripe * NS * SZ;
     const size_t ldb_bytes = (size_t)ldb * SZ;
 
@@ -184,12 +190,12 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             if (lane == 0) mbar_expect_tx(bar, Cfg::A_BYTES + BN * RB);
             if (lane < BN) bulk_g2s(st + Cfg::A_BYTES + lane * RBS, grow + (unsigned long long)(unsigned)idx_next * ldb_b, RB, bar);
             else if (lane == BN) bulk_g2s(st, a_tile, Cfg::A_BYTES, bar);
-            a_tile += Cfg::A_BYTES;
+            a_tile += TS * Cfg::A_BYTES;
         }
         else
         {
             if (lane * 16 < Cfg::A_BYTES) cp_async16s(st + lane * 16, a_src);
-            a_src += Cfg::A_BYTES;
+            a_src += TS * Cfg::A_BYTES;
             const int idx_mine = idx_next;
 #pragma unroll
             for (int it = 0; it < ITERS; it++)
@@ -199,7 +205,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
                 cp_async16s(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b);
             }
         }
-        idx_ptr += BN;
+        idx_ptr += TS * BN;
         if (i + 1 < nt && lane < BN) idx_next = __ldg(idx_ptr);
     };
     // byte offset of 16-byte chunk `chunk` of gathered row k inside the B part of a slot
@@ -303,6 +309,29 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     }
 
     if (!ok) return;
+    if constexpr (COOP)
+    {
+        // warps 1-3 hand their partial block to warp 0 through the (now idle) rings, lane-major
+        static_assert(!BULK, "the cooperative form reuses the rings, which hold mbarriers in the bulk-copy variant");
+        static_assert((WARPS - 1) * 32 * NACC * 16 <= Cfg::SMEM, "partial blocks must fit the rings");
+        float4 *red = reinterpret_cast<float4 *>(smem_raw);
+        __syncthreads();   // every warp is done reading its ring
+        if (warp > 0)
+        {
+#pragma unroll
+            for (int i = 0; i < NACC; i++) red[((warp - 1) * NACC + i) * 32 + lane] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        }
+        __syncthreads();
+        if (warp > 0) return;
+#pragma unroll
+        for (int w = 0; w < WARPS - 1; w++)
+#pragma unroll
+            for (int i = 0; i < NACC; i++)
+            {
+                const float4 v = red[(w * NACC + i) * 32 + lane];
+                acc[i][0] += v.x; acc[i][1] += v.y; acc[i][2] += v.z; acc[i][3] += v.w;
+            }
+    }
     // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
     const size_t ldc = (size_t)ldb;
     float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
@@ -391,17 +420,23 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
     using Cfg = SmallCfg<PREC, CLS, NS>;
     TspClass &c = h->cls[CLS];
     static bool configured[8] = {false};
-    auto kern = k_spmm_small<PREC, CLS, NS>;
+    auto kern = k_spmm_small<PREC, CLS, NS, false>;
+    auto kern_coop = k_spmm_small<PREC, CLS, NS, true>;
     if (!configured[h->device & 7])
     {
         TSP_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        TSP_CUDA(cudaFuncSetAttribute(kern_coop, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         configured[h->device & 7] = true;
     }
     const int nstripes = colB / NS;
     const long long units = (long long)c.ntasks * nstripes;
-    const int grid = (int)((units + WARPS - 1) / WARPS);
-    if (grid == 0) return TSP_OK;
-    kern<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_pack, c.d_tile_colidx,
+    if (units == 0) return TSP_OK;
+    // One warp per unit fills the GPU only when there are several units per resident warp slot; below that (small
+    // matrices) a CTA per unit with the tiles dealt out to its four warps is faster.  Tasks of one or two tiles gain nothing.
+    const long long warp_slots = (long long)h->prop.multiProcessorCount * (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4) * WARPS;
+    const bool coop = units * WARPS <= warp_slots && (long long)c.tilenum >= 3 * (long long)c.ntasks;
+    const int grid = coop ? (int)units : (int)((units + WARPS - 1) / WARPS);
+    (coop ? kern_coop : kern)<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_pack, c.d_tile_colidx,
                                             (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error);
     TSP_CUDA(cudaGetLastError());
     h->launches++;
@@ -425,7 +460,7 @@ void resources_one(TspKernelResources *out)
     using Cfg = SmallCfg<PREC, CLS, NS>;
     cudaFuncAttributes attr;
     memset(&attr, 0, sizeof(attr));
-    cudaFuncGetAttributes(&attr, k_spmm_small<PREC, CLS, NS>);
+    cudaFuncGetAttributes(&attr, k_spmm_small<PREC, CLS, NS, false>);
     out->threads = WARPS * 32;
     out->registers_per_thread = attr.numRegs;
     out->shared_bytes = Cfg::SMEM + (long long)attr.sharedSizeBytes;
