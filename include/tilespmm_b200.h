@@ -43,6 +43,11 @@ int tsp_version(void);
  * (gamma, delta) out.  The decision table is re-derived for B200 and these kernels. */
 void tilespmm_predict_fp16(const double *features, float *gamma, float *delta);
 void tilespmm_predict_tf32(const double *features, float *gamma, float *delta);
+/* The same walk (upstream tilespmm_policy_select, src/model.h:3463-3491) over a caller-supplied table of `nnodes` nodes
+ * of 11 32-bit fields each, {feature, left_feature, right_feature, child0..3, missing_left_mask, cut, left_cut,
+ * right_cut} (src/model.h:9-13), starting at `root`; a negative child -1-a is the leaf of candidate a.  For checking a
+ * refitted table before it is compiled in.  TSP_EINVAL when the table is malformed. */
+int tsp_policy_walk(const void *nodes, int nnodes, int root, const double *features11, float *gamma, float *delta);
 /* upstream features_from_csr (src/model_features.h:31-57); returns 0 when the CSR is inconsistent. */
 int tsp_features_from_csr(int rows, int cols, long long nnz, const int *h_rowptr, double capability, int colB,
                           double *features11);
@@ -69,8 +74,13 @@ int tsp_info(const tsp_handle *h, int *info12, int *shard_rows2);
 
 /* Copies one tiling array to host memory in UPSTREAM layout (src/format.h:4-21): which = 0 orig_row[rows],
  * 1 tile_ptr[tilem+1], 2 tile_nnz[tilenum+1], 3 tile_colidx[tilenum*BN], 4 Blockdense_Val[tilenum*BM*BN]
- * (the device keeps 64-row tiles in tensor-core core-matrix order; the export permutes them back),
- * 5 orig_tile_row_idx[tilem].  h_dst == NULL only queries the size.  *bytes receives the size. */
+ * (the device keeps 64-row tiles as packed records; the export expands them to upstream's dense tiles),
+ * 5 orig_tile_row_idx[tilem].  Arrays with no upstream counterpart, 64-row class only (cls 0): 6 the row masks,
+ * [tilenum][64] words of 16 bits (TF32) or 32 bits (FP16), bit k of word r set when position (r, k) of the tile holds
+ * a stored entry (an explicit zero counts); 7 rec[tilenum+1], offset of every tile's record in 16-byte units with bit
+ * 31 set for a dense record; 8 the records: a packed record is the 64 masks followed by the values of the set
+ * positions in row-major order (padded to 16 bytes), a dense record (more than 128 TF32 / 256 FP16 values) is the
+ * 4 KB tile in tcgen05 core-matrix order.  h_dst == NULL only queries the size.  *bytes receives the size. */
 int tsp_export(const tsp_handle *h, int cls, int which, void *h_dst, long long *bytes);
 
 /* ---- load balancing.  upstream get_optimal_prefetch_th (src/csr2tile.h:437-642) with the resource table of
@@ -108,6 +118,16 @@ int tsp_tune(tsp_handle *h, const void *d_b, float *d_c, int colB_padded, int *b
  * (src/csr2tile.h:1024) the caller does not have to clear C: panels without tiles are written as zeros and
  * the rows of split panels are cleared by a kernel of this call.  stream is a cudaStream_t (NULL = legacy). */
 int tsp_spmm(tsp_handle *h, const void *d_b, float *d_c, int colB_padded, void *stream);
+/* tsp_spmm only enqueues.  The tcgen05 kernels bound every device-side wait (upstream's kernels have none); when one
+ * runs out the kernel records it, frees its tensor memory and returns early, leaving its part of C incomplete.
+ * tsp_check_error waits for `stream` (NULL: the whole device) and returns TSP_ETIMEOUT if that happened in any launch
+ * of this handle since the last check, TSP_OK otherwise; it clears the record.  The host-buffer entry points below,
+ * tsp_time, tsp_tune and tsp_run check by themselves. */
+int tsp_check_error(tsp_handle *h, void *stream);
+/* Failure-path self test (no upstream counterpart): runs a one-block kernel that allocates tensor memory and waits
+ * `polls` (1..2^22) polls on an mbarrier nobody arrives on, gives up, frees the tensor memory and returns.  The call
+ * must return TSP_ETIMEOUT and leave the handle fully usable; nothing hangs, traps or faults. */
+int tsp_selftest_wait_timeout(tsp_handle *h, int polls);
 long long tsp_c_rows(const tsp_handle *h);
 /* Same, with host buffers: copies B to the device, runs, copies the first rowA rows of C back
  * (upstream src/csr2tile.h:839-842, 1020-1032). */
@@ -123,6 +143,9 @@ long long tsp_launch_count(const tsp_handle *h);
 /* Algorithmic bytes of one SpMM in the upstream tile format: bytes3 = {A tiles + column indices, gathered B
  * rows, C}; per class when cls >= 0, all classes when cls < 0. */
 int tsp_algorithmic_bytes(const tsp_handle *h, int cls, int colB_padded, double *bytes3);
+/* Bytes of the tile data as THIS library keeps it in device memory (what its kernels read per column stripe): dense
+ * tiles of the 16/8-row classes, packed records of the 64-row class, column indices. */
+int tsp_tile_bytes(const tsp_handle *h, int cls, double *bytes);
 /* Times `iters` passes of one class kernel alone (cls 0..2) or of the whole SpMM (cls < 0) with CUDA events
  * on the launching stream; ms = mean per pass. */
 int tsp_time(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB_padded, int iters, float *ms);
@@ -160,12 +183,6 @@ int tsp_load(tsp_handle *h, const char *path);
 int tsp_read_mtx(const char *path, int *m, int *n, long long *nnz, int *is_symmetric, int **h_rowptr, int **h_colidx,
                  float **h_val);
 void tsp_free_host(void *p);
-
-/* ---- measurement aid (no upstream counterpart): the rate, in GB/s, at which all SMs of the device together gather
- * randomly chosen row segments of row_bytes (128, 256 or 512) from a zero-filled buffer of buffer_bytes with plain
- * 16-byte loads.  With a buffer of the size of the dense operand B this is the ceiling of the gather in the SpMM
- * kernels, which read every gathered row from L2. */
-int tsp_probe_gather(int device, int row_bytes, long long buffer_bytes, double *gb_per_s);
 
 #ifdef __cplusplus
 }

@@ -184,9 +184,8 @@ def test_transposed_tcgen05_variant_of_the_small_kernels():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
 
-def test_cusparse_algorithms_and_gather_probe():
-    """The stronger cuSPARSE baselines (CSR_ALG1..3) give the same product as upstream's ALG_DEFAULT, and the gather
-    probe answers with a plausible rate."""
+def test_cusparse_algorithms():
+    """The stronger cuSPARSE baselines (CSR_ALG1..3) give the same product as upstream's ALG_DEFAULT."""
     import numpy as np
     from tilespmm_b200 import api, synth
     rp, ci, v, shape = synth.fixed_nnz_per_row(2048, 12, seed=11)
@@ -200,5 +199,3 @@ def test_cusparse_algorithms_and_gather_probe():
             assert out3[1] > 0 and out3[2] > 0
             ref = c if ref is None else ref
             np.testing.assert_array_equal(c, ref)     # small integers: exact in every algorithm
-    gbs = api.probe_gather(512, 64 << 20)
-    assert 1000.0 < gbs < 40000.0

@@ -157,3 +157,142 @@ def test_tile_cache_round_trip(tmp_path):
         bad = tmp_path / "junk.bin"
         bad.write_bytes(b"not a cache")
         assert r.L.tsp_load(r.h, str(bad).encode()) == 1
+
+
+# ---------------------------------------------------------------- packed records of the 64-row class
+
+def _frag16(prec, r, c):
+    """Position of (r, c) of a 16-row block in mma.sync A-fragment order (upstream src/csr2tile.h:289-307)."""
+    if prec == 0:
+        return ((((r & 7) << 2) + ((c & 7) >> 1)) << 3) + ((c >> 3) << 2) + ((r >> 3) << 1) + (c & 1)
+    return ((((r & 7) << 2) + (c & 3)) << 2) + ((c >> 2) << 1) + (r >> 3)
+
+
+def _upstream64(prec, r, c):
+    """Position of (r, c) inside a 64-row tile as upstream stores it (src/csr2tile.h:319-372)."""
+    kw = 16 if prec == 0 else 8
+    return ((r >> 4) * 2 + c // kw) * 16 * kw + _frag16(prec, r & 15, c % kw)
+
+
+def _umma64(prec, r, k):
+    """Position of (r, k) in the K-major core-matrix order tcgen05.mma reads (dense records)."""
+    t = 8 if prec == 0 else 4
+    return ((k // t) * 8 + (r >> 3)) * 8 * t + (r & 7) * t + (k % t)
+
+
+def masks_from_csr(prec, shape, rp, ci, o):
+    """Ground truth of the row masks, from the CSR and the checker's tiling alone: bit k of masks[tile, r] is set when
+    the CSR stores an entry (whatever its value) at row panel_row + r in the column tile_colidx[tile, k] names."""
+    bn = _orc.BN(prec, 0)
+    rows, tp = o.array(0, "panel_row"), o.array(0, "tile_ptr")
+    masks = np.zeros((int(tp[-1]) if tp.size else 0, 64), dtype=np.uint32)
+    for p, r0 in enumerate(rows):
+        r1 = min(int(r0) + 64, shape[0])
+        cols = ci[rp[r0]:rp[r1]]
+        rank = np.searchsorted(np.unique(cols), cols)
+        rr = np.repeat(np.arange(r0, r1), np.diff(rp[r0:r1 + 1])) - r0
+        np.bitwise_or.at(masks, (tp[p] + rank // bn, rr), (np.uint32(1) << (rank % bn).astype(np.uint32)))
+    return masks
+
+
+def dense_from_records(prec, masks, rec, records):
+    """Upstream's dense 64-row tiles rebuilt on the CPU from the exported records (not through the library's own export)."""
+    bn, vt = _orc.BN(prec, 0), (np.uint16 if prec == 0 else np.float32)
+    vsz, mb = (2 if prec == 0 else 4), (256 if prec == 0 else 128)
+    ntile = masks.shape[0]
+    out = np.zeros((ntile, 64 * bn), dtype=vt)
+    r_idx, k_idx = np.meshgrid(np.arange(64), np.arange(bn), indexing="ij")
+    up = _upstream64(prec, r_idx, k_idx)
+    um = _umma64(prec, r_idx, k_idx)
+    for t in range(ntile):
+        off = int(rec[t] & 0x7fffffff) * 16
+        if rec[t] >> 31:
+            tile = records[off:off + 4096].view(vt)
+            out[t, up.ravel()] = tile[um.ravel()]
+            assert int(rec[t + 1] & 0x7fffffff) * 16 - off == 4096
+            continue
+        stored = records[off:off + mb].view(np.uint32 if prec == 0 else np.uint16)
+        assert np.array_equal(stored.astype(np.uint32), masks[t])             # the record starts with the tile's masks
+        set_bits = ((masks[t][:, None] >> np.arange(bn, dtype=np.uint32)[None, :]) & 1).astype(bool)   # [64, bn], row-major
+        n = int(set_bits.sum())
+        assert n <= (256 if prec == 0 else 128)
+        assert int(rec[t + 1] & 0x7fffffff) * 16 - off == mb + (n * vsz + 15) // 16 * 16
+        vals = records[off + mb:off + mb + n * vsz].view(vt)
+        out[t, up[set_bits]] = vals
+        assert not records[off + mb + n * vsz:int(rec[t + 1] & 0x7fffffff) * 16].any()   # padding is zero
+    return out.ravel()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_packed_records_of_the_64_row_class(prec):
+    """Row masks against the CSR ground truth (an explicit zero sets its bit), record offsets and contents against
+    upstream's dense tiles, for sparse tiles (packed records), fuller tiles (dense records) and repeated entries."""
+    from tilespmm_b200 import api
+    picks = [("stencil_g17", (0.0, 1.5)), ("mixed_4096", (0.0, 1.5)), ("banded_4099", (1.0, 1.0)), ("rand_dups_150", (0.0, 1.5)),
+             ("rand_wide_64x5000", (0.0, 1.5)), ("rmat_s11", (1.4, 1.5)), ("rand_tiny_5", (0.0, 1.5))]
+    m = api.TileMatrix(prec)
+    kinds = set()
+    for name, (g, d) in picks:
+        rp, ci, v, shape = CASES[name]
+        v = v.copy()
+        v[::7] = 0.0                                            # stored zeros: present in the masks, absent from the values
+        m.convert_host(shape, rp, ci, v, g, d)
+        info = m.info()
+        o = _orc.Orc(prec, shape, rp, ci, v, g, d)
+        assert info.tolist() == o.info().tolist()
+        if info[0, 3] == 0:
+            assert m.array(0, "masks").size == 0 and m.array(0, "records").size == 0
+            continue
+        masks = m.array(0, "masks").reshape(-1, 64).astype(np.uint32)
+        np.testing.assert_array_equal(masks, masks_from_csr(prec, shape, rp, ci, o), err_msg=name)
+        rec, records = m.array(0, "rec"), m.array(0, "records")
+        assert rec[0] & 0x7fffffff == 0 and int(rec[-1] & 0x7fffffff) * 16 == records.size
+        kinds |= {bool(x >> 31) for x in rec[:-1]}
+        want = o.array(0, "tile_val")
+        np.testing.assert_array_equal(dense_from_records(prec, masks, rec, records), want, err_msg=name)
+        np.testing.assert_array_equal(m.array(0, "tile_val"), want, err_msg=name)      # the library's own expansion
+    assert kinds == {False, True}                               # both record kinds were exercised
+    m.close()
+
+
+def test_inconsistent_csr_and_damaged_cache_are_refused(tmp_path):
+    """Bad input must come back as TSP_EINVAL before any kernel indexes with it."""
+    import ctypes as C
+    from tilespmm_b200 import api
+    rp, ci, v, shape = CASES["banded_1500"]
+    m = api.TileMatrix(1)
+    for what in ("column", "negative", "rowptr_order", "rowptr_end"):
+        rp2, ci2 = rp.copy(), ci.copy()
+        if what == "column":
+            ci2[ci2.size // 2] = shape[1]
+        elif what == "negative":
+            ci2[3] = -1
+        elif what == "rowptr_order":
+            rp2[10], rp2[11] = rp2[11] + 5, rp2[10]
+        else:
+            rp2[-1] -= 1
+        with pytest.raises(api.TileSpMMError, match="inconsistent"):
+            m.convert_host(shape, rp2, ci2, v, 2.0, 1.2)
+    m.convert_host(shape, rp, ci, v, 0.0, 1.5)                  # the handle is still usable
+    m.info()
+    path = tmp_path / "tiles.bin"
+    m.L.tsp_save.argtypes = [C.c_void_p, C.c_char_p]
+    m.L.tsp_load.argtypes = [C.c_void_p, C.c_char_p]
+    assert m.L.tsp_save(m.h, str(path).encode()) == 0
+    good = path.read_bytes()
+    hdr = 112                                                   # sizeof(FileHeader) in csrc/tile_cache.cu; tilem[0] sits at byte 52
+    tilem = int(m.info()[0, 2])
+    col_at = hdr + (tilem + 1) * 4 + tilem * 4 + (int(m.info()[0, 3]) + 1) * 4      # first column index of the 64-row class
+    damaged = {
+        "truncated": good[:len(good) // 2],
+        "negative count": good[:52] + (-5).to_bytes(4, "little", signed=True) + good[56:],
+        "column": good[:col_at] + (shape[1] + 7).to_bytes(4, "little") + good[col_at + 4:],
+        "tile pointer": good[:hdr + 4] + (10 ** 6).to_bytes(4, "little") + good[hdr + 8:],
+    }
+    r = api.TileMatrix(1)
+    for what, blob in damaged.items():
+        bad = tmp_path / "bad.bin"
+        bad.write_bytes(blob)
+        assert r.L.tsp_load(r.h, str(bad).encode()) == 1, what
+    assert r.L.tsp_load(r.h, str(path).encode()) == 0
+    m.close(); r.close()

@@ -4,6 +4,9 @@ import json
 import re
 
 import numpy as np
+import pytest
+
+from tilespmm_b200 import retrain_model as rm
 
 
 def _records():
@@ -61,3 +64,97 @@ def test_shipped_table_answers_a_candidate_through_the_c_abi():
     for prec in (0, 1):
         g, d = api.predict(prec, f)
         assert (round(g, 1), round(d, 1)) in r.CANDIDATES
+
+
+# ---------------------------------------------------------------- the C walker (csrc/model.cu) itself
+
+def _c_walk(nodes, root, features):
+    """tsp_policy_walk over a table given as a list of node dicts (retrain_model's format) -> candidate number or None."""
+    import ctypes as C
+    from tilespmm_b200 import api
+    L = api.lib()
+    L.tsp_policy_walk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    raw = np.zeros((max(len(nodes), 1), 11), dtype=np.int32)
+    for i, n in enumerate(nodes):
+        raw[i, :8] = [n["feature"], n["left_feature"], n["right_feature"], *n["child"], n["mask"]]
+        raw[i, 8:] = np.array([n["cut"], n["left_cut"], n["right_cut"]], dtype=np.float32).view(np.int32)
+    f = np.ascontiguousarray(features, dtype=np.float64)
+    g, d = C.c_float(0), C.c_float(0)
+    rc = L.tsp_policy_walk(raw.ctypes.data_as(C.c_void_p), len(nodes), root, f.ctypes.data_as(C.c_void_p), C.byref(g), C.byref(d))
+    if rc != 0:
+        return None
+    cands = [(np.float32(a), np.float32(b)) for a, b in rm.CANDIDATES]
+    return cands.index((np.float32(g.value), np.float32(d.value)))
+
+
+def _random_table(rng, nnodes):
+    """A well-formed table in upstream's node format: children point to earlier nodes or leaves; about half of the sides
+    carry a second feature; every missing_left_mask combination occurs."""
+    nodes = []
+    for i in range(nnodes):
+        def child():
+            return int(rng.integers(0, i)) if (i > 0 and rng.random() < 0.6) else -1 - int(rng.integers(0, 66))
+        nodes.append({"feature": int(rng.integers(0, 9)), "left_feature": int(rng.integers(0, 9)) if rng.random() < 0.5 else -1,
+                      "right_feature": int(rng.integers(0, 9)) if rng.random() < 0.5 else -1, "child": [child(), child(), child(), child()],
+                      "mask": int(rng.integers(0, 8)), "cut": float(rng.normal()), "left_cut": float(rng.normal()), "right_cut": float(rng.normal())})
+    return nodes
+
+
+def test_c_walker_matches_the_python_walk_on_random_tables_with_second_levels_and_nans():
+    rng = np.random.default_rng(123)
+    checked = nan_routes = second = 0
+    for _ in range(40):
+        nodes = _random_table(rng, int(rng.integers(1, 40)))
+        root = len(nodes) - 1
+        for _ in range(60):
+            f = np.concatenate([[0.0, 0.0], rng.normal(size=9)])
+            f[2 + rng.integers(0, 9, size=int(rng.integers(0, 4)))] = np.nan          # missing features take the mask's side
+            f[2 + int(rng.integers(0, 9))] = nodes[root]["cut"]                            # a value exactly on a cut goes right
+            want = rm.walk(nodes, root, f)
+            assert _c_walk(nodes, root, f) == want
+            checked += 1
+            nan_routes += int(np.isnan(f).any())
+            second += int(nodes[root]["left_feature"] >= 0 or nodes[root]["right_feature"] >= 0)
+    assert checked == 2400 and nan_routes > 500 and second > 500
+
+
+def test_c_walker_refuses_malformed_tables():
+    ok = {"feature": 0, "left_feature": -1, "right_feature": -1, "child": [-1, -1, -2, -2], "mask": 0, "cut": 0.0, "left_cut": 0.0, "right_cut": 0.0}
+    f = np.zeros(11)
+    assert _c_walk([ok], 0, f) == 1                                                     # 0.0 < 0.0 is false: right side, leaf 1
+    assert _c_walk([dict(ok, child=[0, 0, 0, 0])], 0, f) is None                        # a loop
+    assert _c_walk([dict(ok, child=[5, 5, 5, 5])], 0, f) is None                        # a child outside the table
+    assert _c_walk([dict(ok, child=[-100, -100, -100, -100])], 0, f) is None            # a leaf outside the candidates
+    assert _c_walk([dict(ok, feature=12)], 0, f) is None                                # a feature outside the vector
+    assert _c_walk([], -4, f) == 3                                                      # a bare leaf as the root
+
+
+def test_c_walker_reproduces_upstream_on_upstreams_own_table():
+    """The 800 golden answers were produced by upstream's tilespmm_policy_select (src/model.h:3463-3491) on upstream's table.
+    The product's walker, run over that same table (read from oracle/_ref, which compiles upstream's model.h where it
+    lies), must give the same answers -- this pins the walk semantics on a 3421-node table with second-level tests."""
+    import ctypes as C
+    import json
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    lib = os.path.join(os.path.dirname(here), "oracle", "_ref", "libref_model_table.so")
+    if not os.path.exists(lib):
+        pytest.skip("oracle/_ref/libref_model_table.so is not built (needs the upstream checkout)")
+    from tilespmm_b200 import api
+    R = C.CDLL(lib)
+    R.ref_model_nodes.restype = C.c_void_p
+    n, nb, r16, r32 = C.c_int(0), C.c_int(0), C.c_int(0), C.c_int(0)
+    table = R.ref_model_nodes(C.byref(n), C.byref(nb), C.byref(r16), C.byref(r32))
+    assert nb.value == 44 and n.value > 3000
+    L = api.lib()
+    L.tsp_policy_walk.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    golden = json.load(open(os.path.join(here, "golden", "tiling_golden.json")))["model"]
+    assert len(golden) == 800
+    answers = set()
+    for rec in golden:
+        f = np.array(rec["features"], dtype=np.float64)
+        g, d = C.c_float(0), C.c_float(0)
+        rc = L.tsp_policy_walk(C.c_void_p(table), n.value, r32.value if rec["precision"] else r16.value, f.ctypes.data_as(C.c_void_p), C.byref(g), C.byref(d))
+        assert rc == 0 and (g.value, d.value) == (np.float32(rec["gamma"]), np.float32(rec["delta"])), rec
+        answers.add((g.value, d.value))
+    assert len(answers) >= 5                                                            # not a constant function

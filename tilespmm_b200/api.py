@@ -15,6 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TILESPMM_B200_LIB") or os.path.join(HERE, "libtilespmm_b200.so")
 CLASSES = (64, 16, 8)
 ARRAYS = ("orig_row", "tile_ptr", "tile_nnz", "tile_colidx", "tile_val", "panel_row")
+ARRAYS64 = ("masks", "rec", "records")      # 64-row class only: export indices 6, 7, 8
 _lib = None
 
 
@@ -43,6 +44,8 @@ def lib() -> C.CDLL:
         L.tsp_export_schedule.argtypes = [vp, i, C.POINTER(i), vp, vp]
         L.tsp_tune.argtypes = [vp, vp, vp, i, vp, C.POINTER(f)]
         L.tsp_spmm.argtypes = [vp, vp, vp, i, vp]
+        L.tsp_check_error.argtypes = [vp, vp]
+        L.tsp_selftest_wait_timeout.argtypes = [vp, i]
         L.tsp_c_rows.restype = ll
         L.tsp_c_rows.argtypes = [vp]
         L.tsp_spmm_host.argtypes = [vp, vp, vp, i]
@@ -51,9 +54,9 @@ def lib() -> C.CDLL:
         L.tsp_launch_count.restype = ll
         L.tsp_launch_count.argtypes = [vp]
         L.tsp_algorithmic_bytes.argtypes = [vp, i, i, vp]
+        L.tsp_tile_bytes.argtypes = [vp, i, C.POINTER(C.c_double)]
         L.tsp_time.argtypes = [vp, i, vp, vp, i, i, C.POINTER(f)]
         L.tsp_run.argtypes = [vp, vp, vp, i, i, C.c_double, i, vp]
-        L.tsp_probe_gather.argtypes = [i, i, ll, C.POINTER(C.c_double)]
         L.tsp_cusparse_baseline.argtypes = [i, i, i, i, ll, vp, vp, vp, i, i, vp, vp, i, i, vp]
         L.tsp_features_from_csr.argtypes = [i, i, ll, vp, C.c_double, i, vp]
         L.tilespmm_predict_fp16.argtypes = [vp, C.POINTER(f), C.POINTER(f)]
@@ -96,14 +99,6 @@ def features_from_csr(rowptr, shape, capability: float, colB: int) -> np.ndarray
     if not lib().tsp_features_from_csr(shape[0], shape[1], int(rowptr[-1]), _p(rowptr), capability, colB, _p(f)):
         raise TileSpMMError("inconsistent CSR row pointer")
     return f
-
-
-def probe_gather(row_bytes: int, buffer_bytes: int, device: int = 0) -> float:
-    """GB/s at which the device gathers random row segments of row_bytes out of a buffer of buffer_bytes (the
-    L2 side ceiling of the SpMM kernels' gather)."""
-    out = C.c_double(0)
-    _check(lib().tsp_probe_gather(device, row_bytes, buffer_bytes, C.byref(out)), "tsp_probe_gather")
-    return out.value
 
 
 def predict(precision: int, features) -> tuple[float, float]:
@@ -157,11 +152,17 @@ class TileMatrix:
         return out.reshape(3, 4)
 
     def array(self, cls: int, which: str) -> np.ndarray:
-        w = ARRAYS.index(which)
+        w = ARRAYS.index(which) if which in ARRAYS else 6 + ARRAYS64.index(which)
         nbytes = C.c_longlong(0)
         _check(self.L.tsp_export(self.h, cls, w, None, C.byref(nbytes)), "tsp_export")
         if which == "tile_val":
             out = np.zeros(nbytes.value // (4 if self.precision else 2), dtype=np.float32 if self.precision else np.uint16)
+        elif which == "masks":
+            out = np.zeros(nbytes.value // (2 if self.precision else 4), dtype=np.uint16 if self.precision else np.uint32)
+        elif which == "rec":
+            out = np.zeros(nbytes.value // 4, dtype=np.uint32)
+        elif which == "records":
+            out = np.zeros(nbytes.value, dtype=np.uint8)
         else:
             out = np.zeros(nbytes.value // 4, dtype=np.int32)
         if nbytes.value:
@@ -199,6 +200,11 @@ class TileMatrix:
         _check(self.L.tsp_algorithmic_bytes(self.h, cls, colB_padded, _p(out)), "tsp_algorithmic_bytes")
         return out
 
+    def tile_bytes(self, cls: int = -1) -> float:
+        out = C.c_double(0)
+        _check(self.L.tsp_tile_bytes(self.h, cls, C.byref(out)), "tsp_tile_bytes")
+        return out.value
+
     # -- compute
     def tune(self, d_b, d_c, colB_padded: int):
         best = np.zeros(3, dtype=np.int32)
@@ -208,6 +214,10 @@ class TileMatrix:
 
     def spmm(self, d_b, d_c, colB_padded: int, stream: int = 0):
         _check(self.L.tsp_spmm(self.h, _p(d_b), _p(d_c), colB_padded, C.c_void_p(stream)), "tsp_spmm")
+
+    def check_error(self, stream: int = 0):
+        """Waits for `stream` (0: the device) and raises if a bounded wait ran out in a kernel of this handle."""
+        _check(self.L.tsp_check_error(self.h, C.c_void_p(stream) if stream else None), "tsp_check_error")
 
     def spmm_host(self, h_b: np.ndarray, colB_padded: int) -> np.ndarray:
         rows = self.row_range[1] - self.row_range[0] if hasattr(self, "row_range") else self.shape[0]

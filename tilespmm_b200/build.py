@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtilespmm_b200.so")
-SOURCES = ["api.cu", "convert.cu", "sched.cu", "spmm_small.cu", "spmm_small_t.cu", "spmm64.cu", "spmm64_tma.cu", "model.cu", "tile_cache.cu", "probe.cu", "mtx_reader.cpp"]
+SOURCES = ["api.cu", "convert.cu", "sched.cu", "spmm_small.cu", "spmm_small_t.cu", "spmm64.cu", "model.cu", "tile_cache.cu", "selftest.cu", "mtx_reader.cpp"]
 BIN = os.path.join(HERE, "bin")
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-w"]

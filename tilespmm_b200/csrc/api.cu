@@ -96,6 +96,8 @@ extern "C" int tsp_destroy(tsp_handle *h)
     cudaSetDevice(h->device);
     cudaDeviceSynchronize();
     tsp_free_tiles(h);
+    tsp_free_workspace(h);
+    if (h->h_pin) cudaFreeHost(h->h_pin);
     for (int i = 0; i < 2; i++) { if (h->side[i]) cudaStreamDestroy(h->side[i]); if (h->join[i]) cudaEventDestroy(h->join[i]); }
     if (h->fork) cudaEventDestroy(h->fork);
     if (h->t0) cudaEventDestroy(h->t0);
@@ -117,28 +119,14 @@ extern "C" int tsp_convert_device(tsp_handle *h, int rowA, int colA, long long n
                                   const void *d_val, float gamma, float delta, int shard_index, int shard_count)
 {
     if (!h || !d_rowptr || (nnz > 0 && (!d_colidx || !d_val))) { tsp_set_error("convert: null argument"); return TSP_EINVAL; }
-    return tsp_convert_impl(h, rowA, colA, nnz, d_rowptr, d_colidx, d_val, gamma, delta, shard_index, shard_count);
+    return tsp_convert_impl(h, rowA, colA, nnz, d_rowptr, d_colidx, d_val, false, gamma, delta, shard_index, shard_count);
 }
 
 extern "C" int tsp_convert_host(tsp_handle *h, int rowA, int colA, long long nnz, const int *rp, const int *ci, const void *val,
                                 float gamma, float delta, int shard_index, int shard_count)
 {
     if (!h || !rp || rowA <= 0 || nnz < 0 || (nnz > 0 && (!ci || !val))) { tsp_set_error("convert: bad argument"); return TSP_EINVAL; }
-    TSP_CUDA(cudaSetDevice(h->device));
-    const size_t vsz = h->precision ? 4 : 2;
-    int *d_rp = nullptr, *d_ci = nullptr;
-    void *d_v = nullptr;
-    int rc = TSP_OK;
-    cudaError_t e = cudaMalloc((void **)&d_rp, ((size_t)rowA + 1) * 4);
-    if (e == cudaSuccess) e = cudaMalloc((void **)&d_ci, (size_t)(nnz ? nnz : 1) * 4);
-    if (e == cudaSuccess) e = cudaMalloc(&d_v, (size_t)(nnz ? nnz : 1) * vsz);
-    if (e == cudaSuccess) e = cudaMemcpy(d_rp, rp, ((size_t)rowA + 1) * 4, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess && nnz) e = cudaMemcpy(d_ci, ci, (size_t)nnz * 4, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess && nnz) e = cudaMemcpy(d_v, val, (size_t)nnz * vsz, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) { tsp_set_error("convert: upload of the CSR failed: %s", cudaGetErrorString(e)); rc = TSP_ECUDA; }
-    else rc = tsp_convert_impl(h, rowA, colA, nnz, d_rp, d_ci, d_v, gamma, delta, shard_index, shard_count);
-    cudaFree(d_rp); cudaFree(d_ci); cudaFree(d_v);
-    return rc;
+    return tsp_convert_impl(h, rowA, colA, nnz, rp, ci, val, true, gamma, delta, shard_index, shard_count);
 }
 
 extern "C" int tsp_info(const tsp_handle *h, int *info12, int *shard_rows2)
@@ -163,7 +151,7 @@ extern "C" int tsp_export(const tsp_handle *h, int cls, int which, void *dst, lo
     const TspClass &c = h->cls[cls];
     const size_t vsz = h->precision ? 4 : 2;
     *bytes = 0;
-    if (c.rows == 0) return TSP_OK;
+    if (c.rows == 0 && which != 7) return TSP_OK;
     switch (which)
     {
     case 0:  // orig_row: the rows of every panel, in panel order (src/hetero_split.h:86-141)
@@ -194,6 +182,22 @@ extern "C" int tsp_export(const tsp_handle *h, int cls, int which, void *dst, lo
     case 5:
         *bytes = (long long)c.tilem * 4;
         if (dst) memcpy(dst, c.h_panel_row.data(), (size_t)*bytes);
+        return TSP_OK;
+    case 6:  // 64-row class: row masks of every tile
+        if (cls != 0) return TSP_OK;
+        *bytes = (long long)c.tilenum * tsp_mask_bytes(h->precision);
+        if (dst && *bytes) TSP_CUDA(cudaMemcpy(dst, c.d_bitmap, (size_t)*bytes, cudaMemcpyDeviceToHost));
+        return TSP_OK;
+    case 7:  // 64-row class: record offsets
+        if (cls != 0) return TSP_OK;
+        *bytes = ((long long)c.tilenum + 1) * 4;
+        if (dst && c.tilenum) TSP_CUDA(cudaMemcpy(dst, c.d_rec, (size_t)*bytes, cudaMemcpyDeviceToHost));
+        else if (dst) memset(dst, 0, (size_t)*bytes);
+        return TSP_OK;
+    case 8:  // 64-row class: the records
+        if (cls != 0) return TSP_OK;
+        *bytes = c.pack_bytes;
+        if (dst && *bytes) TSP_CUDA(cudaMemcpy(dst, c.d_pack, (size_t)*bytes, cudaMemcpyDeviceToHost));
         return TSP_OK;
     default:
         tsp_set_error("export: unknown array %d", which);
@@ -288,6 +292,25 @@ static int check_device_error(tsp_handle *h)
         return TSP_ETIMEOUT;
     }
     return TSP_OK;
+}
+
+// Waits for `stream` (NULL: the whole device) and reports a bounded wait that ran out in any kernel launched through
+// this handle since the last check.  The flag is cleared, so the next call starts clean.
+extern "C" int tsp_check_error(tsp_handle *h, void *stream)
+{
+    if (!h) { tsp_set_error("check_error: null handle"); return TSP_EINVAL; }
+    TSP_CUDA(cudaSetDevice(h->device));
+    if (stream) TSP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    else TSP_CUDA(cudaDeviceSynchronize());
+    return check_device_error(h);
+}
+
+extern "C" int tsp_selftest_wait_timeout(tsp_handle *h, int polls)
+{
+    if (!h || polls <= 0 || polls > (1 << 22)) { tsp_set_error("selftest_wait_timeout: polls must be in 1..2^22"); return TSP_EINVAL; }
+    TSP_CUDA(cudaSetDevice(h->device));
+    TSP_TRY(tsp_launch_selftest_wait(h, (unsigned)polls, 0));
+    return tsp_check_error(h, nullptr);
 }
 
 extern "C" int tsp_spmm(tsp_handle *h, const void *d_b, float *d_c, int colB, void *stream)
@@ -385,6 +408,22 @@ extern "C" int tsp_algorithmic_bytes(const tsp_handle *h, int cls, int colB, dou
         b3[0] += (double)c.tilenum * (c.BM * c.BN * vsz + c.BN * 4.0);
         b3[1] += (double)c.tilenum * c.BN * colB * vsz;
         b3[2] += (double)c.rows * colB * 4.0;
+    }
+    return TSP_OK;
+}
+
+// Bytes of the tile data as this library stores it and as its kernels read it once per column stripe: values or
+// records plus column indices; per class when cls >= 0, all classes when cls < 0.
+extern "C" int tsp_tile_bytes(const tsp_handle *h, int cls, double *bytes)
+{
+    if (!h || !bytes || cls > 2) { tsp_set_error("tile_bytes: bad argument"); return TSP_EINVAL; }
+    const double vsz = h->precision ? 4 : 2;
+    *bytes = 0.0;
+    for (int k = 0; k < 3; k++)
+    {
+        if (cls >= 0 && cls != k) continue;
+        const TspClass &c = h->cls[k];
+        *bytes += (double)c.tilenum * c.BN * 4.0 + (k == 0 ? (double)c.pack_bytes + ((double)c.tilenum + 1) * 4.0 : (double)c.tilenum * c.BM * c.BN * vsz);
     }
     return TSP_OK;
 }
@@ -562,6 +601,7 @@ extern "C" int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB, int
     if ((rc = tsp_tune(h, d_b, d_c, colB, best3, &tune_ms)) != TSP_OK) return bail(rc);
     if ((rc = spmm_on(h, d_b, d_c, colB, 0)) != TSP_OK) return bail(rc);
     if (cudaDeviceSynchronize() != cudaSuccess) { tsp_set_error("run: checked pass failed: %s", cudaGetErrorString(cudaGetLastError())); return bail(TSP_ECUDA); }
+    if ((rc = check_device_error(h)) != TSP_OK) return bail(rc);
     if (h_c && cudaMemcpy(h_c, d_c, (size_t)(h->row_end - h->row_begin) * colB * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
     {
         tsp_set_error("run: copy of C failed");

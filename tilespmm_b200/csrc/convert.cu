@@ -12,9 +12,16 @@
 //   4. keys (panel, column) -> sort -> unique: sorted distinct columns of every panel; tiles per panel,
 //      prefix sums (tile_ptr), tile_colidx with upstream's padding.
 //   5. one warp per original row: rank of every entry in its panel's column list -> tile, slot; per-tile
-//      entry counts (tile_nnz) and the dense tile values, accumulated in CSR order in value type.
+//      entry counts (tile_nnz); for the 16- and 8-row classes the dense tile values, accumulated in CSR order in
+//      value type; for the 64-row class the row masks of every tile (bitmap).
+//   6. 64-row class: entries per tile from the masks -> record sizes (packed: masks + values, dense: 4 KB) ->
+//      prefix sum (record offsets) -> values placed in mask order (repeated entries summed in CSR order).
 //
-// All outputs are bit-identical to upstream's for the same CSR, gamma and delta.
+// tile_ptr, tile_nnz, tile_colidx, panel rows and, after expansion (tsp_export), the tile values are bit-identical to
+// upstream's for the same CSR, gamma and delta; the masks are defined by the CSR alone (an explicit zero sets its bit).
+//
+// Host side: all scratch comes from a workspace kept in the handle (no cudaMalloc/cudaFree per stage), the tile
+// arrays of all classes are one allocation, and the host reads back a handful of scalars in three small copies.
 #include <cub/cub.cuh>
 
 #include "tsp_internal.cuh"
@@ -24,27 +31,52 @@ namespace
 
 constexpr int CHAIN_L = 512;  // 8-row blocks per chunk of the chain resolution
 
-template <typename T>
-struct DevBuf  // RAII device buffer for conversion scratch
+// Bump allocator over the handle's workspace chunks.  The first conversion sizes chunk 0 from nnz and rowA; what
+// does not fit (sizes known only later) goes into further chunks, which later conversions reuse.
+struct Workspace
 {
-    T *p = nullptr;
-    size_t n = 0;
-    int alloc(size_t count)
+    tsp_handle *h;
+    size_t chunk = 0, used = 0;
+    explicit Workspace(tsp_handle *hh) : h(hh) {}
+    template <typename T>
+    int get(T **p, size_t count)
     {
-        n = count;
-        if (count == 0) count = 1;
-        cudaError_t e = cudaMalloc((void **)&p, count * sizeof(T));
-        if (e != cudaSuccess)
+        size_t bytes = (count * sizeof(T) + 255) & ~(size_t)255;
+        if (bytes == 0) bytes = 256;
+        while (chunk < h->ws_chunks.size() && h->ws_chunks[chunk].second - used < bytes) { chunk++; used = 0; }
+        if (chunk == h->ws_chunks.size())
         {
-            p = nullptr;
-            tsp_set_error("conversion scratch: cudaMalloc of %zu bytes failed: %s", count * sizeof(T), cudaGetErrorString(e));
-            return TSP_ENOMEM;
+            void *q = nullptr;
+            const size_t cap = bytes > ((size_t)8 << 20) ? bytes : ((size_t)8 << 20);
+            cudaError_t e = cudaMalloc(&q, cap);
+            if (e != cudaSuccess)
+            {
+                tsp_set_error("conversion workspace: cudaMalloc of %zu bytes failed: %s", cap, cudaGetErrorString(e));
+                return TSP_ENOMEM;
+            }
+            h->ws_chunks.push_back({q, cap});
+            used = 0;
         }
+        *p = reinterpret_cast<T *>(static_cast<unsigned char *>(h->ws_chunks[chunk].first) + used);
+        used += bytes;
         return TSP_OK;
     }
-    void release() { if (p) cudaFree(p); p = nullptr; }
-    ~DevBuf() { release(); }
 };
+
+int reserve_workspace(tsp_handle *h, size_t bytes)
+{
+    if (!h->ws_chunks.empty() && h->ws_chunks[0].second >= bytes) return TSP_OK;
+    tsp_free_workspace(h);
+    void *q = nullptr;
+    cudaError_t e = cudaMalloc(&q, bytes);
+    if (e != cudaSuccess)
+    {
+        tsp_set_error("conversion workspace: cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        return TSP_ENOMEM;
+    }
+    h->ws_chunks.push_back({q, bytes});
+    return TSP_OK;
+}
 
 __device__ __forceinline__ int lower_bound_dev(const int *a, int n, int key)
 {
@@ -59,24 +91,39 @@ __device__ __forceinline__ int lower_bound_dev(const int *a, int n, int key)
 
 // ---- stage 1
 
-__global__ void k_make_block_keys(int rowA, const int *__restrict__ rowptr, const int *__restrict__ colidx,
-                                  unsigned long long *__restrict__ keys)
+// Keys of all entries, and the consistency check of the CSR: row pointers start at 0, never decrease and end at nnz,
+// every column lies in [0, colA).  A CSR that fails is reported through *bad before anything is indexed with its
+// contents (the row ranges used here are clamped to [0, nnz]); every slot of keys[] is written for a valid CSR.
+__global__ void k_make_block_keys(int rowA, int colA, int nnz, const int *__restrict__ rowptr, const int *__restrict__ colidx,
+                                  unsigned long long *__restrict__ keys, int *__restrict__ bad)
 {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
+    int wrong = 0;
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rowA; r += warps)
     {
-        const int b = rowptr[r], e = rowptr[r + 1];
+        int b = rowptr[r], e = rowptr[r + 1];
+        if (b > e || b < 0 || e > nnz || (r == 0 && b != 0) || (r == rowA - 1 && e != nnz)) wrong = 1;
+        b = min(max(b, 0), nnz); e = min(max(e, b), nnz);
         const unsigned long long hi = (unsigned long long)(r >> 3) << 32;
-        for (int j = b + lane; j < e; j += 32) keys[j] = hi | (unsigned int)colidx[j];
+        for (int j = b + lane; j < e; j += 32)
+        {
+            const int c = colidx[j];
+            if (c < 0 || c >= colA) wrong = 1;
+            keys[j] = hi | (unsigned int)c;
+        }
     }
+    if (wrong) atomicExch(bad, 1);
 }
 
-// first index whose (key >> 32) >= g, for g = 0..ngroups
-__global__ void k_group_offsets(const unsigned long long *__restrict__ keys, int n, int ngroups, int *__restrict__ ptr)
+// first index whose (key >> 32) >= g, for g = 0..ngroups (+ `pad` more entries holding the total)
+__global__ void k_group_offsets(const unsigned long long *__restrict__ keys, const int *__restrict__ n_ptr, int ngroups, int pad,
+                                int *__restrict__ ptr)
 {
     int g = blockIdx.x * blockDim.x + threadIdx.x;
-    if (g > ngroups) return;
+    if (g > ngroups + pad) return;
+    const int n = *n_ptr;
+    if (g > ngroups) { ptr[g] = n; return; }
     int lo = 0, hi = n;
     while (lo < hi)
     {
@@ -86,10 +133,10 @@ __global__ void k_group_offsets(const unsigned long long *__restrict__ keys, int
     ptr[g] = lo;
 }
 
-__global__ void k_low_words(const unsigned long long *__restrict__ keys, int n, int *__restrict__ out)
+__global__ void k_low_words(const unsigned long long *__restrict__ keys, const int *__restrict__ n_ptr, int *__restrict__ out)
 {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = (int)(unsigned int)keys[i];
+    const int n = *n_ptr;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = (int)(unsigned int)keys[i];
 }
 
 // ---- stage 2: distinct columns of windows of 2 and 8 consecutive blocks (one warp per window)
@@ -258,6 +305,69 @@ __global__ void k_make_panel_keys(const unsigned long long *__restrict__ ukeys, 
     out[i] = ((unsigned long long)blk_seq[(int)(k >> 32)] << 32) | (k & 0xffffffffull);
 }
 
+// ---- shard selection on the device: a contiguous range of the panel sequence, balanced by tile bytes
+
+// bytes of one tile (values + indices + gathered rows of a 128-wide B) plus the C rows of the panel and a fixed
+// 12 KB per panel: measured on R-MAT scale 24, starting a task costs about as much as 3 more tiles
+__global__ void k_panel_costs(int nseq, int precision, const int *__restrict__ seq_tiles, const unsigned char *__restrict__ seq_cls,
+                              double *__restrict__ cost)
+{
+    int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= nseq) return;
+    const int k = seq_cls[s], bm = tsp_bm(k), bn = tsp_bn(precision, k), vsz = precision ? 4 : 2;
+    cost[s] = (double)seq_tiles[s] * (bm * bn * vsz + bn * 4 + bn * 128 * vsz) + bm * 128 * 4.0 + 12288.0;
+}
+
+// out[0..1] = s0, s1 (panel range of the shard), out[2..4] / out[5..7] = first / one-past-last class-local panel index
+// (initialised here, completed by k_shard_bounds), out[8..9] = first / one-past-last original row of the shard
+__global__ void k_find_cuts(int nseq, int rowA, int shard_index, int shard_count, const double *__restrict__ prefix /* inclusive */,
+                            const int *__restrict__ seq_blk, int *__restrict__ out)
+{
+    if (blockIdx.x || threadIdx.x) return;
+    const double total = nseq ? prefix[nseq - 1] : 0.0;
+    auto cut = [&](int g) {   // first s whose exclusive prefix is >= total * g / shard_count
+        const double want = total * g / shard_count;
+        int lo = 0, hi = nseq;
+        while (lo < hi) { const int mid = (lo + hi) / 2; const double ex = mid ? prefix[mid - 1] : 0.0; if (ex < want) lo = mid + 1; else hi = mid; }
+        return lo;
+    };
+    int s0 = shard_index == 0 ? 0 : cut(shard_index);
+    int s1 = shard_index == shard_count - 1 ? nseq : cut(shard_index + 1);
+    if (s1 < s0) s1 = s0;
+    out[0] = s0; out[1] = s1;
+    for (int k = 0; k < 3; k++) { out[2 + k] = 0x7fffffff; out[5 + k] = 0; }
+    int rb = s0 < nseq ? seq_blk[s0] * 8 : rowA, re = s1 < nseq ? seq_blk[s1] * 8 : rowA;
+    if (s0 == s1) rb = re;
+    out[8] = rb; out[9] = re;
+}
+
+__global__ void k_shard_bounds(const int *cuts, const unsigned char *__restrict__ seq_cls, const int *__restrict__ seq_idx, int *out)
+{
+    const int s0 = cuts[0], s1 = cuts[1];
+    for (int s = s0 + blockIdx.x * blockDim.x + threadIdx.x; s < s1; s += gridDim.x * blockDim.x)
+    {
+        const int k = seq_cls[s];
+        atomicMin(&out[2 + k], seq_idx[s]);
+        atomicMax(&out[5 + k], seq_idx[s] + 1);
+    }
+}
+
+// rows and stored entries of every class inside the shard
+__global__ void k_class_totals(int s0, int s1, int rowA, const unsigned char *__restrict__ seq_cls, const int *__restrict__ seq_blk,
+                               const int *__restrict__ rowptr, unsigned long long *__restrict__ rows_nnz /* [3][2] */)
+{
+    unsigned long long rows[3] = {0, 0, 0}, nnz[3] = {0, 0, 0};
+    for (int s = s0 + blockIdx.x * blockDim.x + threadIdx.x; s < s1; s += gridDim.x * blockDim.x)
+    {
+        const int k = seq_cls[s];
+        const long long r0 = (long long)seq_blk[s] * 8, r1 = min(r0 + tsp_bm(k), (long long)rowA);
+        rows[k] += (unsigned long long)(r1 - r0);
+        nnz[k] += (unsigned long long)(rowptr[r1] - rowptr[r0]);
+    }
+    for (int k = 0; k < 3; k++)
+        if (rows[k]) { atomicAdd(&rows_nnz[k * 2], rows[k]); atomicAdd(&rows_nnz[k * 2 + 1], nnz[k]); }
+}
+
 __global__ void k_seq_tiles(int nseq, const int *__restrict__ pptr, const unsigned char *__restrict__ seq_cls, int precision,
                             int *__restrict__ seq_tiles)
 {
@@ -312,13 +422,39 @@ __device__ __forceinline__ __half add_in_value_type<__half>(__half a, __half b) 
 template <>
 __device__ __forceinline__ float add_in_value_type<float>(float a, float b) { return __fadd_rn(a, b); }
 
+// Repeated (row, col) entries land on one position and must be added in CSR order (src/csr2tile.h:271, 283, 318):
+// the lowest lane of every group of equal positions adds the group's values in lane order, starting from what the
+// position already holds.  Called by all lanes of a warp; inactive lanes pass a position no other lane has.
+template <typename V>
+__device__ __forceinline__ void add_in_csr_order(V *vals, unsigned long long pos, V v, bool active, int lane)
+{
+    const unsigned int grp = __match_any_sync(0xffffffffu, pos);
+    const bool leader = active && (__ffs(grp) - 1) == lane;
+    int most = __popc(grp);
+    for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+    V acc = V(0.0f);
+    if (leader) acc = vals[pos];
+    unsigned int rest = grp;
+    for (int q = 0; q < most; q++)
+    {
+        const int src = rest ? __ffs(rest) - 1 : lane;
+        const V got = __shfl_sync(0xffffffffu, v, src);
+        if (leader && rest) acc = add_in_value_type<V>(acc, got);
+        rest &= rest - 1;
+    }
+    if (leader) vals[pos] = acc;
+    __syncwarp();
+}
+
+// One warp per original row: tile and slot of every entry; per-tile entry counts (all classes); dense tile values of
+// the 16- and 8-row classes; row masks of the 64-row tiles.
 template <typename V>
 __global__ void k_place_values(int rowA, int precision, int s0, int s1, const int *__restrict__ rowptr, const int *__restrict__ colidx,
                                const V *__restrict__ val, const int *__restrict__ blk_seq, const unsigned char *__restrict__ seq_cls,
                                const int *__restrict__ seq_idx, const int *__restrict__ seq_blk, const int *__restrict__ pptr,
                                const int *__restrict__ pcols, int p0_64, int p0_16, int p0_8, const int *__restrict__ tp64,
                                const int *__restrict__ tp16, const int *__restrict__ tp8, int *tn64, int *tn16, int *tn8,
-                               V *v64, V *v16, V *v8)
+                               unsigned int *__restrict__ mask64 /* 32-bit words of the row masks */, V *v16, V *v8)
 {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -332,7 +468,7 @@ __global__ void k_place_values(int rowA, int precision, int s0, int s1, const in
         const int p = seq_idx[s] - (k == 0 ? p0_64 : (k == 1 ? p0_16 : p0_8));
         const int t0 = (k == 0 ? tp64 : (k == 1 ? tp16 : tp8))[p];
         int *tn = k == 0 ? tn64 : (k == 1 ? tn16 : tn8);
-        V *vals = k == 0 ? v64 : (k == 1 ? v16 : v8);
+        V *vals = k == 1 ? v16 : v8;
         const int ri = r - seq_blk[s] * 8;
         const int g0 = pptr[s], d = pptr[s + 1] - g0;
         for (int base = jb; base < je; base += 32)
@@ -346,64 +482,192 @@ __global__ void k_place_values(int rowA, int precision, int s0, int s1, const in
                 const int rank = lower_bound_dev(pcols + g0, d, colidx[j]);
                 const int t = rank / bn, c = rank - t * bn;
                 atomicAdd(&tn[t0 + t], 1);
-                pos = (unsigned long long)(t0 + t) * (unsigned long long)(bm * bn) + (unsigned long long)tsp_device_index(precision, k, ri, c);
-                v = val[j];
+                if (k == 0)
+                {
+                    // row mask of (tile, row): 16-bit masks (TF32) are addressed as halves of 32-bit words
+                    const size_t bit = ((size_t)(t0 + t) * 64 + ri) * bn + c;
+                    atomicOr(&mask64[bit >> 5], 1u << (bit & 31));
+                }
+                else
+                {
+                    pos = (unsigned long long)(t0 + t) * (unsigned long long)(bm * bn) + (unsigned long long)tsp_upstream_index(precision, k, ri, c);
+                    v = val[j];
+                }
             }
-            // Repeated (row, col) entries land on one position and must be added in CSR order
-            // (src/csr2tile.h:271, 283, 318): the lowest lane of every group of equal positions adds the
-            // group's values in lane order.
-            const unsigned int grp = __match_any_sync(0xffffffffu, pos);
-            const bool leader = active && (__ffs(grp) - 1) == lane;
-            int most = __popc(grp);
-            for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
-            V acc = V(0.0f);
-            if (leader) acc = vals[pos];
-            unsigned int rest = grp;
-            for (int q = 0; q < most; q++)
-            {
-                const int src = rest ? __ffs(rest) - 1 : lane;
-                const V got = __shfl_sync(0xffffffffu, v, src);
-                if (leader && rest) acc = add_in_value_type<V>(acc, got);
-                rest &= rest - 1;
-            }
-            if (leader) vals[pos] = acc;
-            __syncwarp();
+            if (k != 0) add_in_csr_order<V>(vals, pos, v, active, lane);
         }
     }
 }
 
-// 64-row tiles back to the upstream order (sub-blocks in mma.sync fragment order, src/csr2tile.h:319-372)
-template <typename V>
-__global__ void k_export64(int precision, long long nelem, const V *__restrict__ src, V *__restrict__ dst)
+// ---- stage 6: packed records of the 64-row class
+
+// One warp per tile: entries of the tile from its masks -> record size in 16-byte units (dense 4 KB record above
+// TSP_REC_MAX_VALS values), the dense flag, and the number of values before every row (row_off, 64 per tile).
+__global__ void k_rec_sizes(int tilenum, int precision, const unsigned int *__restrict__ mask64, unsigned int *__restrict__ units,
+                            unsigned char *__restrict__ dense, unsigned short *__restrict__ row_off)
 {
-    const int bn = tsp_bn(precision, 0), per = 64 * bn;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nelem; i += (long long)gridDim.x * blockDim.x)
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int vsz = precision ? 4 : 2, max_vals = TSP_REC_MAX_VALS(precision), mask_bytes = tsp_mask_bytes(precision);
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tilenum; t += warps)
     {
-        const long long tile = i / per;
-        const int e = (int)(i - tile * per), r = e / bn, c = e - r * bn;
-        dst[tile * per + tsp_upstream_index(precision, 0, r, c)] = src[tile * per + tsp_umma_index(precision, r, c)];
+        // lane l owns rows 2l and 2l+1
+        unsigned int w0, w1;
+        if (precision) { const unsigned int w = mask64[(size_t)t * 32 + lane]; w0 = w & 0xffffu; w1 = w >> 16; }
+        else { w0 = mask64[(size_t)t * 64 + 2 * lane]; w1 = mask64[(size_t)t * 64 + 2 * lane + 1]; }
+        const int c0 = __popc(w0), cnt = c0 + __popc(w1);
+        int incl = cnt;
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        row_off[(size_t)t * 64 + 2 * lane] = (unsigned short)(incl - cnt);
+        row_off[(size_t)t * 64 + 2 * lane + 1] = (unsigned short)(incl - cnt + c0);
+        if (lane == 0)
+        {
+            const bool is_dense = total > max_vals;
+            dense[t] = is_dense ? 1 : 0;
+            units[t] = is_dense ? (64u * tsp_bn(precision, 0) * vsz) / 16u : (unsigned int)(mask_bytes + ((total * vsz + 15) & ~15)) / 16u;
+        }
+    }
+}
+
+// rec[t] = exclusive prefix of the record sizes with the dense flag in bit 31; rec[tilenum] = total; units[] holds the
+// exclusive prefix on entry.
+__global__ void k_rec_finish(int tilenum, const unsigned int *__restrict__ prefix, const unsigned char *__restrict__ dense,
+                             unsigned int *__restrict__ rec)
+{
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t > tilenum) return;
+    rec[t] = prefix[t] | (t < tilenum && dense[t] ? 0x80000000u : 0u);
+}
+
+// Row masks into the head of every packed record.
+__global__ void k_copy_masks(int tilenum, int precision, const unsigned int *__restrict__ mask64, const unsigned int *__restrict__ rec,
+                             unsigned char *__restrict__ pack)
+{
+    const int words = tsp_mask_bytes(precision) / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)tilenum * words; i += (long long)gridDim.x * blockDim.x)
+    {
+        const int t = (int)(i / words), w = (int)(i - (long long)t * words);
+        const unsigned int r = rec[t];
+        if (r >> 31) continue;
+        reinterpret_cast<unsigned int *>(pack + (size_t)r * 16)[w] = mask64[i];
+    }
+}
+
+// One warp per original row of the 64-row class: every entry's value goes to its place in the tile's record -- the
+// position given by the masks for a packed record, the operand position for a dense one.
+template <typename V>
+__global__ void k_place_values64(int rowA, int precision, int s0, int s1, const int *__restrict__ rowptr, const int *__restrict__ colidx,
+                                 const V *__restrict__ val, const int *__restrict__ blk_seq, const unsigned char *__restrict__ seq_cls,
+                                 const int *__restrict__ seq_idx, const int *__restrict__ seq_blk, const int *__restrict__ pptr,
+                                 const int *__restrict__ pcols, int p0_64, const int *__restrict__ tp64, const unsigned int *__restrict__ mask64,
+                                 const unsigned short *__restrict__ row_off, const unsigned int *__restrict__ rec, V *__restrict__ pack)
+{
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int bn = tsp_bn(precision, 0), mask_elems = tsp_mask_bytes(precision) / (int)sizeof(V), per16 = 16 / (int)sizeof(V);
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rowA; r += warps)
+    {
+        const int s = blk_seq[r >> 3];
+        if (s < s0 || s >= s1 || seq_cls[s] != 0) continue;
+        const int jb = rowptr[r], je = rowptr[r + 1];
+        if (jb == je) continue;
+        const int t0 = tp64[seq_idx[s] - p0_64];
+        const int ri = r - seq_blk[s] * 8;
+        const int g0 = pptr[s], d = pptr[s + 1] - g0;
+        for (int base = jb; base < je; base += 32)
+        {
+            const int j = base + lane;
+            const bool active = j < je;
+            unsigned long long pos = ~0ull - (unsigned long long)lane;
+            V v = V(0.0f);
+            if (active)
+            {
+                const int rank = lower_bound_dev(pcols + g0, d, colidx[j]);
+                const int t = t0 + rank / bn, c = rank % bn;
+                const unsigned int rw = rec[t];
+                const unsigned long long rec_elem = (unsigned long long)(rw & 0x7fffffffu) * per16;
+                if (rw >> 31) pos = rec_elem + (unsigned long long)tsp_umma_index(precision, ri, c);
+                else
+                {
+                    const size_t bit = ((size_t)t * 64 + ri) * bn;          // first bit of the row mask
+                    unsigned int m = mask64[bit >> 5] >> (bit & 31);
+                    if (precision) m &= 0xffffu;
+                    pos = rec_elem + mask_elems + row_off[(size_t)t * 64 + ri] + __popc(m & ((1u << c) - 1u));
+                }
+                v = val[j];
+            }
+            add_in_csr_order<V>(pack, pos, v, active, lane);
+        }
+    }
+}
+
+// 64-row tiles as upstream stores them (dense, sub-blocks in mma.sync fragment order, src/csr2tile.h:319-372), expanded
+// from the records; dst is zero-filled by the caller.  One warp per tile, lane l owns rows 2l and 2l+1.
+template <typename V>
+__global__ void k_export64(int tilenum, int precision, const unsigned int *__restrict__ rec, const unsigned char *__restrict__ pack,
+                           V *__restrict__ dst)
+{
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int bn = tsp_bn(precision, 0), per = 64 * bn, mask_bytes = tsp_mask_bytes(precision);
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tilenum; t += warps)
+    {
+        const unsigned int rw = rec[t];
+        const unsigned char *record = pack + (size_t)(rw & 0x7fffffffu) * 16;
+        V *out = dst + (size_t)t * per;
+        if (rw >> 31)
+        {
+            const V *src = reinterpret_cast<const V *>(record);
+            for (int e = lane; e < per; e += 32) { const int r = e / bn, c = e - r * bn; out[tsp_upstream_index(precision, 0, r, c)] = src[tsp_umma_index(precision, r, c)]; }
+            continue;
+        }
+        unsigned int w0, w1;
+        const unsigned int *masks = reinterpret_cast<const unsigned int *>(record);
+        if (precision) { const unsigned int w = masks[lane]; w0 = w & 0xffffu; w1 = w >> 16; }
+        else { w0 = masks[2 * lane]; w1 = masks[2 * lane + 1]; }
+        const int cnt = __popc(w0) + __popc(w1);
+        int incl = cnt;
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+        const V *src = reinterpret_cast<const V *>(record + mask_bytes) + (incl - cnt);
+        for (int half = 0; half < 2; half++)
+        {
+            unsigned int w = half ? w1 : w0;
+            while (w) { const int c = __ffs(w) - 1; w &= w - 1; out[tsp_upstream_index(precision, 0, 2 * lane + half, c)] = *src++; }
+        }
     }
 }
 
 inline int blocks_for(long long n, int threads) { return (int)((n + threads - 1) / threads > 0 ? (n + threads - 1) / threads : 1); }
 
-int sort_unique_keys(DevBuf<unsigned long long> &keys, DevBuf<unsigned long long> &tmp, int n, int key_bits, int *n_unique)
+// Radix sort on the bits in use, then unique.  keys/tmp are swapped so that the result is in `keys`; the number of
+// distinct keys is left in *d_count (device).
+int sort_unique_keys(unsigned long long *&keys, unsigned long long *&tmp, int n, int key_bits, void *scratch, size_t scratch_bytes,
+                     int *d_count)
 {
-    // radix sort on the bits in use, then unique; result left in `keys`
-    DevBuf<unsigned char> scratch;
-    DevBuf<int> d_count;
-    TSP_TRY(d_count.alloc(1));
-    size_t bytes_sort = 0, bytes_uniq = 0;
-    cub::DoubleBuffer<unsigned long long> db(keys.p, tmp.p);
-    TSP_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, bytes_sort, db, n, 0, key_bits));
-    TSP_CUDA(cub::DeviceSelect::Unique(nullptr, bytes_uniq, keys.p, tmp.p, d_count.p, n));
-    TSP_TRY(scratch.alloc(bytes_sort > bytes_uniq ? bytes_sort : bytes_uniq));
-    TSP_CUDA(cub::DeviceRadixSort::SortKeys(scratch.p, bytes_sort, db, n, 0, key_bits));
+    cub::DoubleBuffer<unsigned long long> db(keys, tmp);
+    size_t bytes = scratch_bytes;
+    TSP_CUDA(cub::DeviceRadixSort::SortKeys(scratch, bytes, db, n, 0, key_bits));
     unsigned long long *sorted = db.Current(), *other = db.Alternate();
-    TSP_CUDA(cub::DeviceSelect::Unique(scratch.p, bytes_uniq, sorted, other, d_count.p, n));
-    TSP_CUDA(cudaMemcpy(n_unique, d_count.p, sizeof(int), cudaMemcpyDeviceToHost));
-    if (other != keys.p) { unsigned long long *t = keys.p; keys.p = tmp.p; tmp.p = t; }
+    bytes = scratch_bytes;
+    TSP_CUDA(cub::DeviceSelect::Unique(scratch, bytes, sorted, other, d_count, n));
+    keys = other; tmp = sorted;
     return TSP_OK;
+}
+
+size_t sort_unique_scratch_bytes(int n)
+{
+    size_t a = 0, b = 0;
+    cub::DoubleBuffer<unsigned long long> db(nullptr, nullptr);
+    cub::DeviceRadixSort::SortKeys(nullptr, a, db, n, 0, 64);
+    cub::DeviceSelect::Unique(nullptr, b, (unsigned long long *)nullptr, (unsigned long long *)nullptr, (int *)nullptr, n);
+    size_t c = 0, d = 0;   // the prefix sums over panels share the same scratch
+    cub::DeviceScan::ExclusiveSum(nullptr, c, (int *)nullptr, (int *)nullptr, n + 1);
+    cub::DeviceScan::InclusiveSum(nullptr, d, (double *)nullptr, (double *)nullptr, n + 1);
+    if (b > a) a = b;
+    if (c > a) a = c;
+    if (d > a) a = d;
+    return a + 256;
 }
 
 int bits_for(unsigned long long v)
@@ -413,14 +677,29 @@ int bits_for(unsigned long long v)
     return b;
 }
 
+// small pinned host buffer for scalar read-backs
+int pinned(tsp_handle *h, int **p)
+{
+    if (!h->h_pin) TSP_CUDA(cudaMallocHost(&h->h_pin, 4096));
+    *p = static_cast<int *>(h->h_pin);
+    return TSP_OK;
+}
+
 }  // namespace
+
+void tsp_free_workspace(tsp_handle *h)
+{
+    for (auto &c : h->ws_chunks) cudaFree(c.first);
+    h->ws_chunks.clear();
+}
 
 void tsp_free_tiles(tsp_handle *h)
 {
+    cudaFree(h->tile_block); cudaFree(h->pack_block);
+    h->tile_block = h->pack_block = nullptr;
     for (int k = 0; k < 3; k++)
     {
         TspClass &c = h->cls[k];
-        cudaFree(c.d_tile_ptr); cudaFree(c.d_tile_nnz); cudaFree(c.d_tile_colidx); cudaFree(c.d_panel_row); cudaFree(c.d_val);
         cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_split_row); cudaFree(c.d_task_count); cudaFree(c.d_task_pack);
         c = TspClass();
         c.BM = tsp_bm(k);
@@ -428,6 +707,63 @@ void tsp_free_tiles(tsp_handle *h)
     }
     h->converted = false;
     h->bmap_ptr = nullptr;
+}
+
+// One allocation for every tile array of the three classes; sizes come from cls[k].tilem and cls[k].tilenum.
+// tile_ptr (inputs of a scan), tile_nnz (atomic counters), the dense values and the masks start as zeros.
+int tsp_alloc_tile_arrays(tsp_handle *h)
+{
+    const size_t vsz = h->precision ? 4 : 2;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += (bytes + 255) & ~(size_t)255; return at; };
+    size_t at[3][7];
+    for (int k = 0; k < 3; k++)
+    {
+        const TspClass &c = h->cls[k];
+        at[k][0] = take(((size_t)c.tilem + 1) * 4);                                   // tile_ptr
+        at[k][1] = take(((size_t)c.tilem + 1) * 4);                                   // panel_row
+        at[k][2] = take(((size_t)c.tilenum + 1) * 4);                                 // tile_nnz
+        at[k][3] = take(((size_t)c.tilenum * c.BN + 4) * 4);                          // tile_colidx
+        at[k][4] = k == 0 ? take((size_t)c.tilenum * tsp_mask_bytes(h->precision) + 16)   // masks
+                          : take((size_t)c.tilenum * c.BM * c.BN * vsz + 16);         // dense values
+        at[k][5] = k == 0 ? take(((size_t)c.tilenum + 1) * 4) : 0;                    // rec
+    }
+    cudaFree(h->tile_block);
+    h->tile_block = nullptr;
+    cudaError_t e = cudaMalloc(&h->tile_block, off);
+    if (e != cudaSuccess) { tsp_set_error("tile arrays: cudaMalloc of %zu bytes failed: %s", off, cudaGetErrorString(e)); return TSP_ENOMEM; }
+    unsigned char *base = static_cast<unsigned char *>(h->tile_block);
+    for (int k = 0; k < 3; k++)
+    {
+        TspClass &c = h->cls[k];
+        c.d_tile_ptr = (int *)(base + at[k][0]);
+        c.d_panel_row = (int *)(base + at[k][1]);
+        c.d_tile_nnz = (int *)(base + at[k][2]);
+        c.d_tile_colidx = (int *)(base + at[k][3]);
+        if (k == 0) { c.d_bitmap = base + at[k][4]; c.d_rec = (unsigned int *)(base + at[k][5]); c.d_val = nullptr; }
+        else c.d_val = base + at[k][4];
+    }
+    // zero: everything except the column indices (fully written later); cheaper as a few ranges than as one memset of all
+    for (int k = 0; k < 3; k++)
+    {
+        const size_t from = at[k][0], to = at[k][3];
+        TSP_CUDA(cudaMemsetAsync(base + from, 0, to - from, 0));
+        const size_t vend = k == 2 ? off : at[k + 1][0];
+        TSP_CUDA(cudaMemsetAsync(base + at[k][4], 0, vend - at[k][4], 0));
+    }
+    return TSP_OK;
+}
+
+int tsp_alloc_pack(tsp_handle *h, long long bytes)
+{
+    cudaFree(h->pack_block);
+    h->pack_block = nullptr;
+    cudaError_t e = cudaMalloc(&h->pack_block, (size_t)bytes + 16);
+    if (e != cudaSuccess) { tsp_set_error("64-row records: cudaMalloc of %lld bytes failed: %s", bytes, cudaGetErrorString(e)); return TSP_ENOMEM; }
+    TSP_CUDA(cudaMemsetAsync(h->pack_block, 0, (size_t)bytes + 16, 0));
+    h->cls[0].d_pack = static_cast<unsigned char *>(h->pack_block);
+    h->cls[0].pack_bytes = bytes;
+    return TSP_OK;
 }
 
 int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst)
@@ -441,18 +777,24 @@ int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst)
         TSP_CUDA(cudaMemcpy(h_dst, c.d_val, nelem * vsz, cudaMemcpyDeviceToHost));
         return TSP_OK;
     }
-    DevBuf<unsigned char> tmp;
-    TSP_TRY(tmp.alloc(nelem * vsz));
-    const int blocks = (int)(nelem / 256 + 1 > 65535 ? 65535 : nelem / 256 + 1);
-    if (h->precision == 0) k_export64<__half><<<blocks, 256>>>(0, nelem, (const __half *)c.d_val, (__half *)tmp.p);
-    else k_export64<float><<<blocks, 256>>>(1, nelem, (const float *)c.d_val, (float *)tmp.p);
-    TSP_CUDA(cudaGetLastError());
-    TSP_CUDA(cudaMemcpy(h_dst, tmp.p, nelem * vsz, cudaMemcpyDeviceToHost));
+    void *tmp = nullptr;
+    TSP_CUDA(cudaMalloc(&tmp, nelem * vsz));
+    cudaError_t e = cudaMemset(tmp, 0, nelem * vsz);
+    const int blocks = c.tilenum / 8 + 1 > 148 * 16 ? 148 * 16 : c.tilenum / 8 + 1;
+    if (e == cudaSuccess)
+    {
+        if (h->precision == 0) k_export64<__half><<<blocks, 256>>>(c.tilenum, 0, c.d_rec, c.d_pack, (__half *)tmp);
+        else k_export64<float><<<blocks, 256>>>(c.tilenum, 1, c.d_rec, c.d_pack, (float *)tmp);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(h_dst, tmp, nelem * vsz, cudaMemcpyDeviceToHost);
+    cudaFree(tmp);
+    TSP_CUDA(e);
     return TSP_OK;
 }
 
-int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const int *d_rowptr, const int *d_colidx,
-                     const void *d_val, float gamma, float delta, int shard_index, int shard_count)
+int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const int *rowptr_in, const int *colidx_in,
+                     const void *val_in, bool csr_on_host, float gamma, float delta, int shard_index, int shard_count)
 {
     if (rowA <= 0 || colA <= 0 || nnz64 < 0 || nnz64 > 0x7fffffffLL || shard_count < 1 || shard_index < 0 || shard_index >= shard_count)
     {
@@ -466,6 +808,10 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     const int prec = h->precision;
     const int nb8 = (rowA + 7) / 8;
     const int T = 256;
+    const int nchunk = (nb8 + CHAIN_L - 1) / CHAIN_L;
+    cudaStream_t st = 0;
+    int *pin = nullptr;
+    TSP_TRY(pinned(h, &pin));
 
     int fixed = -1;  // src/hetero_split.h:152-169
     if (gamma <= 0.0f) fixed = 0;
@@ -474,221 +820,261 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     const bool want64 = fixed < 0 && gamma < 4.0f;
     const bool want16 = fixed < 0 && (want64 || (delta > 0.0f && !(delta > 2.0f)));
 
+    // ---- workspace: everything whose size follows from nnz and rowA, in one chunk
+    const size_t cub_bytes = sort_unique_scratch_bytes(nnz > nb8 + 2 ? nnz : nb8 + 2);
+    {
+        const size_t n = (size_t)(nnz ? nnz : 1), b = (size_t)nb8 + 16;
+        size_t need = 2 * n * 8 + 2 * n * 4 + b * (4 * 9 + 3) + (size_t)nchunk * (8 + 96 + 4 + 12) + b * 8 + cub_bytes + 64 * 256 + (1 << 16);
+        if (csr_on_host) need += ((size_t)rowA + 1) * 4 + n * (4 + (prec ? 4 : 2)) + 1024;
+        TSP_TRY(reserve_workspace(h, need));
+    }
+    Workspace ws(h);
+    const int *d_rowptr = rowptr_in, *d_colidx = colidx_in;
+    const void *d_val = val_in;
+    if (csr_on_host)   // upload of the CSR into the workspace
+    {
+        int *rp, *ci;
+        unsigned char *vv;
+        const size_t vsz = prec ? 4 : 2;
+        TSP_TRY(ws.get(&rp, (size_t)rowA + 1)); TSP_TRY(ws.get(&ci, nnz)); TSP_TRY(ws.get(&vv, (size_t)nnz * vsz));
+        TSP_CUDA(cudaMemcpyAsync(rp, rowptr_in, ((size_t)rowA + 1) * 4, cudaMemcpyHostToDevice, st));
+        if (nnz) TSP_CUDA(cudaMemcpyAsync(ci, colidx_in, (size_t)nnz * 4, cudaMemcpyHostToDevice, st));
+        if (nnz) TSP_CUDA(cudaMemcpyAsync(vv, val_in, (size_t)nnz * vsz, cudaMemcpyHostToDevice, st));
+        d_rowptr = rp; d_colidx = ci; d_val = vv;
+    }
+    unsigned long long *keys, *keys_tmp, *class_rows_nnz;
+    int *u8_ptr, *ucols, *n16, *n64, *entry, *base, *counts, *seq_blk, *seq_idx, *blk_seq, *scalars, *pptr_buf, *pcols_buf, *seq_tiles;
+    unsigned char *cls_of, *exit_off, *seq_cls, *cub_tmp;
+    double *cost;
+    TSP_TRY(ws.get(&keys, nnz)); TSP_TRY(ws.get(&keys_tmp, nnz)); TSP_TRY(ws.get(&u8_ptr, (size_t)nb8 + 9)); TSP_TRY(ws.get(&ucols, nnz));
+    TSP_TRY(ws.get(&n16, nb8)); TSP_TRY(ws.get(&n64, nb8)); TSP_TRY(ws.get(&cls_of, nb8));
+    TSP_TRY(ws.get(&exit_off, (size_t)nchunk * 8)); TSP_TRY(ws.get(&counts, (size_t)nchunk * 24)); TSP_TRY(ws.get(&entry, nchunk));
+    TSP_TRY(ws.get(&base, (size_t)nchunk * 3 + 3));
+    TSP_TRY(ws.get(&seq_blk, nb8)); TSP_TRY(ws.get(&seq_cls, nb8)); TSP_TRY(ws.get(&seq_idx, nb8)); TSP_TRY(ws.get(&blk_seq, nb8));
+    TSP_TRY(ws.get(&class_rows_nnz, 6)); TSP_TRY(ws.get(&scalars, 64)); TSP_TRY(ws.get(&cub_tmp, cub_bytes));
+    TSP_TRY(ws.get(&pptr_buf, (size_t)nb8 + 1)); TSP_TRY(ws.get(&pcols_buf, nnz)); TSP_TRY(ws.get(&seq_tiles, nb8));
+    TSP_TRY(ws.get(&cost, nb8));
+    // scalars: [0] distinct (8-row block, column) pairs, [1] CSR check, [2] distinct (panel, column) pairs, [8..17] shard cuts
+    int *d_nu = scalars, *d_bad = scalars + 1, *d_np = scalars + 2, *d_cuts = scalars + 8;
+    TSP_CUDA(cudaMemsetAsync(scalars, 0, 64 * sizeof(int), st));
+    TSP_CUDA(cudaMemsetAsync(class_rows_nnz, 0, 6 * sizeof(unsigned long long), st));
+
     // ---- stage 1: sorted distinct columns of every 8-row block
-    DevBuf<unsigned long long> keys, keys_tmp;
-    DevBuf<int> u8_ptr, ucols;
-    TSP_TRY(keys.alloc(nnz)); TSP_TRY(keys_tmp.alloc(nnz)); TSP_TRY(u8_ptr.alloc((size_t)nb8 + 9));
-    int nu = 0;
-    if (nnz > 0)
     {
-        k_make_block_keys<<<blocks_for((long long)rowA * 32, T) > 65535 * 4 ? 65535 * 4 : blocks_for((long long)rowA * 32, T), T>>>(rowA, d_rowptr, d_colidx, keys.p);
+        const int blocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
+        k_make_block_keys<<<blocks, T, 0, st>>>(rowA, colA, nnz, d_rowptr, d_colidx, keys, d_bad);   // also checks the row pointers of an empty matrix
         TSP_CUDA(cudaGetLastError());
-        TSP_TRY(sort_unique_keys(keys, keys_tmp, nnz, 32 + bits_for((unsigned long long)nb8), &nu));
+        if (nnz > 0) TSP_TRY(sort_unique_keys(keys, keys_tmp, nnz, 32 + bits_for((unsigned long long)nb8), cub_tmp, cub_bytes, d_nu));
     }
-    k_group_offsets<<<blocks_for(nb8 + 1, T), T>>>(keys.p, nu, nb8, u8_ptr.p);
-    TSP_CUDA(cudaGetLastError());
-    // windows near the end index u8_ptr past nb8: pad with the total
-    {
-        std::vector<int> pad(8, nu);
-        TSP_CUDA(cudaMemcpy(u8_ptr.p + nb8 + 1, pad.data(), 8 * sizeof(int), cudaMemcpyHostToDevice));
-    }
-    TSP_TRY(ucols.alloc(nu));
-    if (nu) k_low_words<<<blocks_for(nu, T), T>>>(keys.p, nu, ucols.p);
+    k_group_offsets<<<blocks_for(nb8 + 9, T), T, 0, st>>>(keys, d_nu, nb8, 8, u8_ptr);   // windows near the end index past nb8
+    if (nnz > 0) k_low_words<<<blocks_for(nnz, T) > 148 * 16 ? 148 * 16 : blocks_for(nnz, T), T, 0, st>>>(keys, d_nu, ucols);
     TSP_CUDA(cudaGetLastError());
 
     // ---- stage 2 + 3: window counts, decisions, chain
-    DevBuf<int> n16, n64, entry, base, counts, seq_blk, seq_idx, blk_seq;
-    DevBuf<unsigned char> cls_of, exit_off, seq_cls;
-    DevBuf<unsigned long long> class_rows_nnz;
-    TSP_TRY(n16.alloc(nb8)); TSP_TRY(n64.alloc(nb8)); TSP_TRY(cls_of.alloc(nb8));
     if (want16 || want64)
     {
-        TSP_CUDA(cudaMemset(n16.p, 0, (size_t)nb8 * 4)); TSP_CUDA(cudaMemset(n64.p, 0, (size_t)nb8 * 4));
+        TSP_CUDA(cudaMemsetAsync(n16, 0, (size_t)nb8 * 4, st)); TSP_CUDA(cudaMemsetAsync(n64, 0, (size_t)nb8 * 4, st));
         const int blocks = blocks_for((long long)nb8 * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)nb8 * 32, T);
-        k_window_counts<<<blocks, T>>>(nb8, rowA, u8_ptr.p, ucols.p, n16.p, n64.p, want64 ? 1 : 0);
+        k_window_counts<<<blocks, T, 0, st>>>(nb8, rowA, u8_ptr, ucols, n16, n64, want64 ? 1 : 0);
         TSP_CUDA(cudaGetLastError());
     }
-    k_decide<<<blocks_for(nb8, T), T>>>(nb8, rowA, gamma, delta, fixed, u8_ptr.p, n16.p, n64.p, cls_of.p);
+    k_decide<<<blocks_for(nb8, T), T, 0, st>>>(nb8, rowA, gamma, delta, fixed, u8_ptr, n16, n64, cls_of);
+    k_chain_local<<<blocks_for((long long)nchunk * 8, T), T, 0, st>>>(nb8, nchunk, cls_of, exit_off, counts);
+    k_chain_compose<<<1, 32, 0, st>>>(nchunk, exit_off, counts, entry, base);
+    k_chain_emit<<<blocks_for(nchunk, 128), 128, 0, st>>>(nb8, nchunk, rowA, cls_of, entry, base, d_rowptr, seq_blk, seq_cls, seq_idx, blk_seq,
+                                                        class_rows_nnz);
     TSP_CUDA(cudaGetLastError());
-    const int nchunk = (nb8 + CHAIN_L - 1) / CHAIN_L;
-    TSP_TRY(exit_off.alloc((size_t)nchunk * 8)); TSP_TRY(counts.alloc((size_t)nchunk * 24)); TSP_TRY(entry.alloc(nchunk));
-    TSP_TRY(base.alloc((size_t)nchunk * 3 + 3));
-    k_chain_local<<<blocks_for((long long)nchunk * 8, T), T>>>(nb8, nchunk, cls_of.p, exit_off.p, counts.p);
-    k_chain_compose<<<1, 32>>>(nchunk, exit_off.p, counts.p, entry.p, base.p);
-    TSP_CUDA(cudaGetLastError());
-    int totals[3];
-    TSP_CUDA(cudaMemcpy(totals, base.p + (size_t)nchunk * 3, sizeof(totals), cudaMemcpyDeviceToHost));
+    // read-back 1: distinct count, CSR check, panels per class, rows and entries per class
+    TSP_CUDA(cudaMemcpyAsync(pin, scalars, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    TSP_CUDA(cudaMemcpyAsync(pin + 2, base + (size_t)nchunk * 3, 3 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    TSP_CUDA(cudaMemcpyAsync(pin + 8, class_rows_nnz, 6 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+    TSP_CUDA(cudaStreamSynchronize(st));
+    const int nu = pin[0];
+    if (pin[1])
+    {
+        tsp_set_error("convert: the CSR is inconsistent (row pointers must start at 0, not decrease and end at nnz; columns must lie in [0, %d))", colA);
+        return TSP_EINVAL;
+    }
+    const int totals[3] = {pin[2], pin[3], pin[4]};
+    unsigned long long tot_rows_nnz[6];
+    memcpy(tot_rows_nnz, pin + 8, sizeof(tot_rows_nnz));
     const int nseq = totals[0] + totals[1] + totals[2];
-    TSP_TRY(seq_blk.alloc(nseq)); TSP_TRY(seq_cls.alloc(nseq)); TSP_TRY(seq_idx.alloc(nseq)); TSP_TRY(blk_seq.alloc(nb8));
-    TSP_TRY(class_rows_nnz.alloc(6));
-    TSP_CUDA(cudaMemset(class_rows_nnz.p, 0, 6 * sizeof(unsigned long long)));
-    k_chain_emit<<<blocks_for(nchunk, 128), 128>>>(nb8, nchunk, rowA, cls_of.p, entry.p, base.p, d_rowptr, seq_blk.p, seq_cls.p,
-                                                  seq_idx.p, blk_seq.p, class_rows_nnz.p);
-    TSP_CUDA(cudaGetLastError());
 
     // ---- stage 4: sorted distinct columns of every panel
-    DevBuf<int> pptr_buf, pcols_buf, seq_tiles;
     const int *pptr = nullptr, *pcols = nullptr;
     const bool all8 = totals[0] == 0 && totals[1] == 0;
-    if (all8) { pptr = u8_ptr.p; pcols = ucols.p; }  // an 8-row panel is one 8-row block
+    if (all8) { pptr = u8_ptr; pcols = ucols; }  // an 8-row panel is one 8-row block
     else
     {
-        int np = 0;
         if (nu)
         {
-            k_make_panel_keys<<<blocks_for(nu, T), T>>>(keys.p, nu, blk_seq.p, keys_tmp.p);
+            k_make_panel_keys<<<blocks_for(nu, T), T, 0, st>>>(keys, nu, blk_seq, keys_tmp);
             TSP_CUDA(cudaGetLastError());
-            { unsigned long long *t = keys.p; keys.p = keys_tmp.p; keys_tmp.p = t; }
-            TSP_TRY(sort_unique_keys(keys, keys_tmp, nu, 32 + bits_for((unsigned long long)nseq), &np));
+            { unsigned long long *t = keys; keys = keys_tmp; keys_tmp = t; }
+            TSP_TRY(sort_unique_keys(keys, keys_tmp, nu, 32 + bits_for((unsigned long long)nseq), cub_tmp, cub_bytes, d_np));
         }
-        TSP_TRY(pptr_buf.alloc((size_t)nseq + 1)); TSP_TRY(pcols_buf.alloc(np));
-        k_group_offsets<<<blocks_for(nseq + 1, T), T>>>(keys.p, np, nseq, pptr_buf.p);
-        if (np) k_low_words<<<blocks_for(np, T), T>>>(keys.p, np, pcols_buf.p);
+        k_group_offsets<<<blocks_for(nseq + 1, T), T, 0, st>>>(keys, d_np, nseq, 0, pptr_buf);
+        if (nu) k_low_words<<<blocks_for(nu, T) > 148 * 16 ? 148 * 16 : blocks_for(nu, T), T, 0, st>>>(keys, d_np, pcols_buf);
         TSP_CUDA(cudaGetLastError());
-        pptr = pptr_buf.p; pcols = pcols_buf.p;
-        ucols.release();
+        pptr = pptr_buf; pcols = pcols_buf;
     }
-    keys.release(); keys_tmp.release();
-    TSP_TRY(seq_tiles.alloc(nseq));
-    if (nseq) k_seq_tiles<<<blocks_for(nseq, T), T>>>(nseq, pptr, seq_cls.p, prec, seq_tiles.p);
+    if (nseq) k_seq_tiles<<<blocks_for(nseq, T), T, 0, st>>>(nseq, pptr, seq_cls, prec, seq_tiles);
     TSP_CUDA(cudaGetLastError());
 
-    // ---- shard selection: a contiguous range of the panel sequence, balanced by tile bytes
-    std::vector<int> h_seq_tiles(nseq), h_seq_blk(nseq), h_seq_idx(nseq);
-    std::vector<unsigned char> h_seq_cls(nseq);
-    if (nseq)
-    {
-        TSP_CUDA(cudaMemcpy(h_seq_tiles.data(), seq_tiles.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost));
-        TSP_CUDA(cudaMemcpy(h_seq_blk.data(), seq_blk.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost));
-        TSP_CUDA(cudaMemcpy(h_seq_idx.data(), seq_idx.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost));
-        TSP_CUDA(cudaMemcpy(h_seq_cls.data(), seq_cls.p, (size_t)nseq, cudaMemcpyDeviceToHost));
-    }
-    int s0 = 0, s1 = nseq;
+    // ---- shard selection: a contiguous range of the panel sequence, balanced by tile bytes (on the device)
+    int s0 = 0, s1 = nseq, p0[3] = {0, 0, 0}, p1[3] = {totals[0], totals[1], totals[2]};
+    h->row_begin = 0; h->row_end = rowA;
     if (shard_count > 1)
     {
-        const size_t vsz = prec ? 4 : 2;
-        std::vector<double> prefix((size_t)nseq + 1, 0.0);
-        for (int s = 0; s < nseq; s++)
+        if (nseq)
         {
-            const int k = h_seq_cls[s], bm = tsp_bm(k), bn = tsp_bn(prec, k);
-            // bytes of one tile (values + indices + gathered rows of a 128-wide B) plus the C rows of the panel and a
-            // fixed 12 KB per panel: measured on R-MAT scale 24, starting a task costs about as much as 3 more tiles
-            prefix[s + 1] = prefix[s] + (double)h_seq_tiles[s] * (bm * bn * vsz + bn * 4 + bn * 128 * vsz) + bm * 128 * 4.0 + 12288.0;
+            k_panel_costs<<<blocks_for(nseq, T), T, 0, st>>>(nseq, prec, seq_tiles, seq_cls, cost);
+            size_t bytes = cub_bytes;
+            TSP_CUDA(cub::DeviceScan::InclusiveSum(cub_tmp, bytes, cost, cost, nseq, st));
         }
-        auto cut = [&](int g) {
-            const double want = prefix[nseq] * g / shard_count;
-            int lo = 0, hi = nseq;
-            while (lo < hi) { int mid = (lo + hi) / 2; if (prefix[mid] < want) lo = mid + 1; else hi = mid; }
-            return lo;
-        };
-        s0 = shard_index == 0 ? 0 : cut(shard_index);
-        s1 = shard_index == shard_count - 1 ? nseq : cut(shard_index + 1);
-        if (s1 < s0) s1 = s0;
+        k_find_cuts<<<1, 32, 0, st>>>(nseq, rowA, shard_index, shard_count, cost, seq_blk, d_cuts);
+        k_shard_bounds<<<blocks_for(nseq ? nseq : 1, T) > 148 * 8 ? 148 * 8 : blocks_for(nseq ? nseq : 1, T), T, 0, st>>>(d_cuts, seq_cls, seq_idx, d_cuts);
+        TSP_CUDA(cudaGetLastError());
+        // read-back 2 (sharded conversions only): the cuts
+        TSP_CUDA(cudaMemcpyAsync(pin, d_cuts, 10 * sizeof(int), cudaMemcpyDeviceToHost, st));
+        TSP_CUDA(cudaStreamSynchronize(st));
+        s0 = pin[0]; s1 = pin[1];
+        for (int k = 0; k < 3; k++)
+        {
+            p0[k] = pin[2 + k]; p1[k] = pin[5 + k];
+            if (p1[k] <= p0[k] || p0[k] == 0x7fffffff) { p0[k] = 0; p1[k] = 0; }
+        }
+        h->row_begin = pin[8]; h->row_end = pin[9];
+        TSP_CUDA(cudaMemsetAsync(class_rows_nnz, 0, 6 * sizeof(unsigned long long), st));
+        if (s1 > s0)
+        {
+            k_class_totals<<<blocks_for(s1 - s0, T) > 148 * 8 ? 148 * 8 : blocks_for(s1 - s0, T), T, 0, st>>>(s0, s1, rowA, seq_cls, seq_blk, d_rowptr,
+                                                                                                              class_rows_nnz);
+            TSP_CUDA(cudaGetLastError());
+        }
     }
-    h->row_begin = s0 < nseq ? h_seq_blk[s0] * 8 : rowA;
-    h->row_end = s1 < nseq ? h_seq_blk[s1] * 8 : rowA;
-    if (s0 == s1) h->row_begin = h->row_end;
+    for (int k = 0; k < 3; k++) h->cls[k].tilem = p1[k] - p0[k];
 
-    int p0[3] = {0, 0, 0}, p1[3] = {0, 0, 0};
-    {
-        bool seen[3] = {false, false, false};
-        for (int k = 0; k < 3; k++) { p0[k] = -1; p1[k] = -1; }
-        for (int s = s0; s < s1; s++)
-        {
-            const int k = h_seq_cls[s];
-            if (!seen[k]) { seen[k] = true; p0[k] = h_seq_idx[s]; }
-            p1[k] = h_seq_idx[s] + 1;
-        }
-        for (int k = 0; k < 3; k++) if (!seen[k]) { p0[k] = 0; p1[k] = 0; }
-    }
+    // ---- tile_ptr: tiles per panel into a workspace array per class, prefix sums; read-back 3: tiles per class
+    int *cnt[3], *prow[3], *tptr[3];
     for (int k = 0; k < 3; k++)
     {
-        TspClass &c = h->cls[k];
-        c.tilem = p1[k] - p0[k];
-        TSP_CUDA(cudaMalloc((void **)&c.d_tile_ptr, ((size_t)c.tilem + 1) * 4));
-        TSP_CUDA(cudaMemset(c.d_tile_ptr, 0, ((size_t)c.tilem + 1) * 4));
-        TSP_CUDA(cudaMalloc((void **)&c.d_panel_row, ((size_t)c.tilem + 1) * 4));
+        TSP_TRY(ws.get(&cnt[k], (size_t)h->cls[k].tilem + 1)); TSP_TRY(ws.get(&prow[k], (size_t)h->cls[k].tilem + 1));
+        TSP_TRY(ws.get(&tptr[k], (size_t)h->cls[k].tilem + 1));
+        TSP_CUDA(cudaMemsetAsync(cnt[k], 0, ((size_t)h->cls[k].tilem + 1) * 4, st));
     }
     if (s1 > s0)
     {
-        k_class_arrays<<<blocks_for(s1 - s0, T), T>>>(s0, s1, seq_tiles.p, seq_cls.p, seq_idx.p, seq_blk.p, p0[0], p0[1], p0[2],
-                                                      h->cls[0].d_tile_ptr, h->cls[1].d_tile_ptr, h->cls[2].d_tile_ptr,
-                                                      h->cls[0].d_panel_row, h->cls[1].d_panel_row, h->cls[2].d_panel_row);
+        k_class_arrays<<<blocks_for(s1 - s0, T), T, 0, st>>>(s0, s1, seq_tiles, seq_cls, seq_idx, seq_blk, p0[0], p0[1], p0[2], cnt[0], cnt[1], cnt[2],
+                                                           prow[0], prow[1], prow[2]);
         TSP_CUDA(cudaGetLastError());
     }
     for (int k = 0; k < 3; k++)
     {
         TspClass &c = h->cls[k];
-        size_t bytes = 0;
-        TSP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, c.d_tile_ptr, c.d_tile_ptr, c.tilem + 1));
-        DevBuf<unsigned char> scratch;
-        TSP_TRY(scratch.alloc(bytes));
-        TSP_CUDA(cub::DeviceScan::ExclusiveSum(scratch.p, bytes, c.d_tile_ptr, c.d_tile_ptr, c.tilem + 1));
+        size_t bytes = cub_bytes;
+        TSP_CUDA(cub::DeviceScan::ExclusiveSum(cub_tmp, bytes, cnt[k], tptr[k], c.tilem + 1, st));
         c.h_tile_ptr.resize((size_t)c.tilem + 1);
         c.h_panel_row.resize(c.tilem);
-        TSP_CUDA(cudaMemcpy(c.h_tile_ptr.data(), c.d_tile_ptr, ((size_t)c.tilem + 1) * 4, cudaMemcpyDeviceToHost));
-        if (c.tilem) TSP_CUDA(cudaMemcpy(c.h_panel_row.data(), c.d_panel_row, (size_t)c.tilem * 4, cudaMemcpyDeviceToHost));
-        c.tilenum = c.h_tile_ptr[c.tilem];
-        // rows and nnz of the class inside the shard
-        c.rows = 0; c.nnz = 0;
-        const size_t vsz = prec ? 4 : 2;
-        TSP_CUDA(cudaMalloc((void **)&c.d_tile_nnz, ((size_t)c.tilenum + 1) * 4));
-        TSP_CUDA(cudaMemset(c.d_tile_nnz, 0, ((size_t)c.tilenum + 1) * 4));
-        TSP_CUDA(cudaMalloc((void **)&c.d_tile_colidx, ((size_t)c.tilenum * c.BN + 1) * 4));
-        TSP_CUDA(cudaMalloc((void **)&c.d_val, (size_t)c.tilenum * c.BM * c.BN * vsz + 16));
-        TSP_CUDA(cudaMemset(c.d_val, 0, (size_t)c.tilenum * c.BM * c.BN * vsz + 16));
+        TSP_CUDA(cudaMemcpyAsync(c.h_tile_ptr.data(), tptr[k], ((size_t)c.tilem + 1) * 4, cudaMemcpyDeviceToHost, st));
+        if (c.tilem) TSP_CUDA(cudaMemcpyAsync(c.h_panel_row.data(), prow[k], (size_t)c.tilem * 4, cudaMemcpyDeviceToHost, st));
     }
-    // class rows / nnz: whole-matrix totals come from the chain; per-shard ones from the host panel lists
+    if (shard_count > 1) TSP_CUDA(cudaMemcpyAsync(pin + 8, class_rows_nnz, 6 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+    TSP_CUDA(cudaStreamSynchronize(st));
+    if (shard_count > 1) memcpy(tot_rows_nnz, pin + 8, sizeof(tot_rows_nnz));
+    for (int k = 0; k < 3; k++)
     {
-        std::vector<int> h_rowptr_ends;  // only needed per shard: compute on device totals when unsharded
-        unsigned long long tot[6];
-        TSP_CUDA(cudaMemcpy(tot, class_rows_nnz.p, sizeof(tot), cudaMemcpyDeviceToHost));
-        if (shard_count == 1)
-            for (int k = 0; k < 3; k++) { h->cls[k].rows = (int)tot[k * 2]; h->cls[k].nnz = (long long)tot[k * 2 + 1]; }
-        else
-        {
-            std::vector<int> h_rowptr((size_t)rowA + 1);
-            TSP_CUDA(cudaMemcpy(h_rowptr.data(), d_rowptr, ((size_t)rowA + 1) * 4, cudaMemcpyDeviceToHost));
-            for (int k = 0; k < 3; k++)
-                for (int p = 0; p < h->cls[k].tilem; p++)
-                {
-                    const int r0 = h->cls[k].h_panel_row[p], r1 = r0 + h->cls[k].BM < rowA ? r0 + h->cls[k].BM : rowA;
-                    h->cls[k].rows += r1 - r0;
-                    h->cls[k].nnz += h_rowptr[r1] - h_rowptr[r0];
-                }
-        }
+        TspClass &c = h->cls[k];
+        c.tilenum = c.h_tile_ptr[c.tilem];
+        c.rows = (int)tot_rows_nnz[k * 2];
+        c.nnz = (long long)tot_rows_nnz[k * 2 + 1];
+    }
+
+    // ---- the tile arrays of all classes: one allocation
+    TSP_TRY(tsp_alloc_tile_arrays(h));
+    for (int k = 0; k < 3; k++)
+    {
+        TspClass &c = h->cls[k];
+        TSP_CUDA(cudaMemcpyAsync(c.d_tile_ptr, tptr[k], ((size_t)c.tilem + 1) * 4, cudaMemcpyDeviceToDevice, st));
+        if (c.tilem) TSP_CUDA(cudaMemcpyAsync(c.d_panel_row, prow[k], (size_t)c.tilem * 4, cudaMemcpyDeviceToDevice, st));
     }
     if (s1 > s0)
     {
         const int blocks = blocks_for((long long)(s1 - s0) * 32, T) > 148 * 32 ? 148 * 32 : blocks_for((long long)(s1 - s0) * 32, T);
-        k_fill_colidx<<<blocks, T>>>(s0, s1, prec, pptr, pcols, seq_cls.p, seq_idx.p, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr,
-                                     h->cls[1].d_tile_ptr, h->cls[2].d_tile_ptr, h->cls[0].d_tile_colidx, h->cls[1].d_tile_colidx,
-                                     h->cls[2].d_tile_colidx);
+        k_fill_colidx<<<blocks, T, 0, st>>>(s0, s1, prec, pptr, pcols, seq_cls, seq_idx, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr,
+                                            h->cls[1].d_tile_ptr, h->cls[2].d_tile_ptr, h->cls[0].d_tile_colidx, h->cls[1].d_tile_colidx,
+                                            h->cls[2].d_tile_colidx);
         TSP_CUDA(cudaGetLastError());
         // ---- stage 5
         const int vblocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
         if (prec == 0)
-            k_place_values<__half><<<vblocks, T>>>(rowA, 0, s0, s1, d_rowptr, d_colidx, (const __half *)d_val, blk_seq.p, seq_cls.p, seq_idx.p,
-                                                   seq_blk.p, pptr, pcols, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr, h->cls[1].d_tile_ptr,
-                                                   h->cls[2].d_tile_ptr, h->cls[0].d_tile_nnz, h->cls[1].d_tile_nnz, h->cls[2].d_tile_nnz,
-                                                   (__half *)h->cls[0].d_val, (__half *)h->cls[1].d_val, (__half *)h->cls[2].d_val);
+            k_place_values<__half><<<vblocks, T, 0, st>>>(rowA, 0, s0, s1, d_rowptr, d_colidx, (const __half *)d_val, blk_seq, seq_cls, seq_idx,
+                                                          seq_blk, pptr, pcols, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr, h->cls[1].d_tile_ptr,
+                                                          h->cls[2].d_tile_ptr, h->cls[0].d_tile_nnz, h->cls[1].d_tile_nnz, h->cls[2].d_tile_nnz,
+                                                          (unsigned int *)h->cls[0].d_bitmap, (__half *)h->cls[1].d_val, (__half *)h->cls[2].d_val);
         else
-            k_place_values<float><<<vblocks, T>>>(rowA, 1, s0, s1, d_rowptr, d_colidx, (const float *)d_val, blk_seq.p, seq_cls.p, seq_idx.p,
-                                                  seq_blk.p, pptr, pcols, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr, h->cls[1].d_tile_ptr,
-                                                  h->cls[2].d_tile_ptr, h->cls[0].d_tile_nnz, h->cls[1].d_tile_nnz, h->cls[2].d_tile_nnz,
-                                                  (float *)h->cls[0].d_val, (float *)h->cls[1].d_val, (float *)h->cls[2].d_val);
+            k_place_values<float><<<vblocks, T, 0, st>>>(rowA, 1, s0, s1, d_rowptr, d_colidx, (const float *)d_val, blk_seq, seq_cls, seq_idx,
+                                                         seq_blk, pptr, pcols, p0[0], p0[1], p0[2], h->cls[0].d_tile_ptr, h->cls[1].d_tile_ptr,
+                                                         h->cls[2].d_tile_ptr, h->cls[0].d_tile_nnz, h->cls[1].d_tile_nnz, h->cls[2].d_tile_nnz,
+                                                         (unsigned int *)h->cls[0].d_bitmap, (float *)h->cls[1].d_val, (float *)h->cls[2].d_val);
         TSP_CUDA(cudaGetLastError());
     }
     for (int k = 0; k < 3; k++)  // tile_nnz: exclusive scan over tilenum+1 entries (src/csr2tile.h:786)
     {
         TspClass &c = h->cls[k];
         size_t bytes = 0;
-        TSP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, c.d_tile_nnz, c.d_tile_nnz, c.tilenum + 1));
-        DevBuf<unsigned char> scratch;
-        TSP_TRY(scratch.alloc(bytes));
-        TSP_CUDA(cub::DeviceScan::ExclusiveSum(scratch.p, bytes, c.d_tile_nnz, c.d_tile_nnz, c.tilenum + 1));
+        TSP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, c.d_tile_nnz, c.d_tile_nnz, c.tilenum + 1, st));
+        void *tmp = cub_tmp;
+        if (bytes > cub_bytes) { unsigned char *more; TSP_TRY(ws.get(&more, bytes)); tmp = more; }
+        TSP_CUDA(cub::DeviceScan::ExclusiveSum(tmp, bytes, c.d_tile_nnz, c.d_tile_nnz, c.tilenum + 1, st));
     }
-    TSP_CUDA(cudaDeviceSynchronize());
+
+    // ---- stage 6: records of the 64-row class
+    {
+        TspClass &c = h->cls[0];
+        c.d_pack = nullptr; c.pack_bytes = 0;
+        if (c.tilenum > 0)
+        {
+            unsigned int *units, *prefix;
+            unsigned char *dense;
+            unsigned short *row_off;
+            TSP_TRY(ws.get(&units, (size_t)c.tilenum + 1)); TSP_TRY(ws.get(&prefix, (size_t)c.tilenum + 1)); TSP_TRY(ws.get(&dense, c.tilenum));
+            TSP_TRY(ws.get(&row_off, (size_t)c.tilenum * 64));
+            TSP_CUDA(cudaMemsetAsync(units + c.tilenum, 0, 4, st));
+            const int wblocks = blocks_for((long long)c.tilenum * 32, T) > 148 * 32 ? 148 * 32 : blocks_for((long long)c.tilenum * 32, T);
+            k_rec_sizes<<<wblocks, T, 0, st>>>(c.tilenum, prec, (const unsigned int *)c.d_bitmap, units, dense, row_off);
+            size_t bytes = 0;
+            TSP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, bytes, units, prefix, c.tilenum + 1, st));
+            void *tmp = cub_tmp;
+            if (bytes > cub_bytes) { unsigned char *more; TSP_TRY(ws.get(&more, bytes)); tmp = more; }
+            TSP_CUDA(cub::DeviceScan::ExclusiveSum(tmp, bytes, units, prefix, c.tilenum + 1, st));
+            k_rec_finish<<<blocks_for(c.tilenum + 1, T), T, 0, st>>>(c.tilenum, prefix, dense, c.d_rec);
+            TSP_CUDA(cudaGetLastError());
+            // read-back 4 (only when there are 64-row tiles): bytes of all records
+            TSP_CUDA(cudaMemcpyAsync(pin, prefix + c.tilenum, 4, cudaMemcpyDeviceToHost, st));
+            TSP_CUDA(cudaStreamSynchronize(st));
+            const long long total_units = (unsigned int)pin[0];
+            if (total_units >= 0x7fffffffLL) { tsp_set_error("convert: the 64-row tile records exceed 32 GB"); return TSP_EINVAL; }
+            TSP_TRY(tsp_alloc_pack(h, total_units * 16));
+            k_copy_masks<<<blocks_for((long long)c.tilenum * 32, T) > 148 * 16 ? 148 * 16 : blocks_for((long long)c.tilenum * 32, T), T, 0, st>>>(
+                c.tilenum, prec, (const unsigned int *)c.d_bitmap, c.d_rec, c.d_pack);
+            const int vblocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
+            if (prec == 0)
+                k_place_values64<__half><<<vblocks, T, 0, st>>>(rowA, 0, s0, s1, d_rowptr, d_colidx, (const __half *)d_val, blk_seq, seq_cls, seq_idx,
+                                                                seq_blk, pptr, pcols, p0[0], c.d_tile_ptr, (const unsigned int *)c.d_bitmap, row_off,
+                                                                c.d_rec, (__half *)c.d_pack);
+            else
+                k_place_values64<float><<<vblocks, T, 0, st>>>(rowA, 1, s0, s1, d_rowptr, d_colidx, (const float *)d_val, blk_seq, seq_cls, seq_idx,
+                                                               seq_blk, pptr, pcols, p0[0], c.d_tile_ptr, (const unsigned int *)c.d_bitmap, row_off,
+                                                               c.d_rec, (float *)c.d_pack);
+            TSP_CUDA(cudaGetLastError());
+        }
+    }
+    TSP_CUDA(cudaStreamSynchronize(st));
+    // a large workspace (hundreds of millions of entries) is given back; a small one stays for the next conversion
+    size_t held = 0;
+    for (auto &ch : h->ws_chunks) held += ch.second;
+    if (held > ((size_t)2 << 30)) tsp_free_workspace(h);
     h->converted = true;
     return TSP_OK;
 }

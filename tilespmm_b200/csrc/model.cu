@@ -29,13 +29,16 @@ struct TspPolicyNode
 
 #include "model_table.inc"
 
-void pick(int root, const double *f, float *gamma, float *delta)
+// Walks `nodes` from `root` (upstream tilespmm_policy_select, src/model.h:3463-3491) and returns the leaf's candidate
+// number, or -1 when the table is malformed (a child outside the table, a loop, a leaf outside the candidates).
+int walk(const TspPolicyNode *nodes, int nnodes, int root, const double *f)
 {
     int index = root;
-    const int nnodes = (int)(sizeof(kPolicyNodes) / sizeof(kPolicyNodes[0]));
-    for (int steps = 0; index >= 0 && index < nnodes && steps < nnodes + 1; steps++)   // a well-formed table never loops
+    for (int steps = 0; index >= 0 && steps < nnodes + 1; steps++)   // a well-formed table never loops
     {
-        const TspPolicyNode &n = kPolicyNodes[index];
+        if (index >= nnodes) return -1;
+        const TspPolicyNode &n = nodes[index];
+        if (n.feature < 0 || n.feature > 8 || n.left_feature > 8 || n.right_feature > 8) return -1;
         float v = (float)f[n.feature + 2];
         const bool left = isnan(v) ? (n.missing_left_mask & 1) != 0 : v < n.cut;
         if (left)
@@ -57,13 +60,32 @@ void pick(int root, const double *f, float *gamma, float *delta)
             }
         }
     }
-    int action = -1 - index;
-    if (action < 0 || action >= 66) action = 3 + 8 * 6 + 5;   // malformed table: the single-rule answer (3.8, 2.0)
+    const int action = -1 - index;
+    return action >= 0 && action < 66 ? action : -1;
+}
+
+void pick(int root, const double *f, float *gamma, float *delta)
+{
+    int action = walk(kPolicyNodes, (int)(sizeof(kPolicyNodes) / sizeof(kPolicyNodes[0])), root, f);
+    if (action < 0) action = 3 + 8 * 6 + 5;   // malformed table: the single-rule answer (3.8, 2.0)
     *gamma = kCandidates[action][0];
     *delta = kCandidates[action][1];
 }
 
 }  // namespace
+
+// The walker on a caller-supplied table: nodes are 11 32-bit fields each, in upstream's order {feature, left_feature,
+// right_feature, child0..3, missing_left_mask, cut, left_cut, right_cut} (src/model.h:9-13).  Lets a refitted table be
+// checked before it is compiled in.  Returns TSP_EINVAL for a malformed table.
+extern "C" int tsp_policy_walk(const void *nodes, int nnodes, int root, const double *features, float *gamma, float *delta)
+{
+    if (!features || !gamma || !delta || nnodes < 0 || (nnodes > 0 && !nodes)) return TSP_EINVAL;
+    const int action = walk(static_cast<const TspPolicyNode *>(nodes), nnodes, root, features);
+    if (action < 0) return TSP_EINVAL;
+    *gamma = kCandidates[action][0];
+    *delta = kCandidates[action][1];
+    return TSP_OK;
+}
 
 extern "C" void tilespmm_predict_fp16(const double *features, float *gamma, float *delta) { pick(kPolicyRootFp16, features, gamma, delta); }
 extern "C" void tilespmm_predict_tf32(const double *features, float *gamma, float *delta) { pick(kPolicyRootTf32, features, gamma, delta); }

@@ -201,7 +201,6 @@ k_spmm_small_t(int ntasks, int nstripes, int ldb /* elements */, int row_begin, 
         if (tid == 0) atomicExch(err, 4);
         return;
     }
-    if (*reinterpret_cast<volatile int *>(err) != 0) return;   // an earlier launch gave up on a wait: do not queue up behind it
     const unsigned bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
     const unsigned bar_acc_full = smem_u32(&bars[2 * S]), bar_acc_empty = smem_u32(&bars[2 * S + 2]);
     const unsigned bar_desc_full = smem_u32(&bars[2 * S + 4]), bar_desc_empty = smem_u32(&bars[2 * S + 4 + R]);

@@ -75,6 +75,11 @@ __host__ __device__ inline int tsp_device_index(int precision, int cls, int r, i
     return cls == 0 ? tsp_umma_index(precision, r, c) : tsp_upstream_index(precision, cls, r, c);
 }
 
+// A 64-row tile with at most this many distinct entries is kept as a packed record (row masks + values), a fuller one
+// as a dense 4 KB tile.
+#define TSP_REC_MAX_VALS(PREC) ((PREC) == 0 ? 256 : 128)
+__host__ __device__ inline int tsp_mask_bytes(int precision) { return precision == 0 ? 256 : 128; }
+
 // Width of the column stripe one task unit covers for (class, padded dense width): the 64-row kernel keeps up to
 // 256 accumulator columns in tensor memory, the 16/8-row kernels up to 128 in registers.
 __host__ __device__ inline int tsp_stripe_width(int cls, int colB)
@@ -99,7 +104,14 @@ struct TspClass
     long long nnz = 0;
     int tilem = 0, tilenum = 0;
     int *d_tile_ptr = nullptr, *d_tile_nnz = nullptr, *d_tile_colidx = nullptr, *d_panel_row = nullptr;
-    void *d_val = nullptr;
+    void *d_val = nullptr;          // dense tiles of the 16- and 8-row classes (upstream fragment order); unused for 64-row tiles
+    // 64-row class only: packed tile records (see spmm64.cu).  d_bitmap[tile][row] = column mask of the row inside the
+    // tile (uint16 for TF32 tiles of 16 columns, uint32 for FP16 tiles of 32 columns); d_rec[tile] = offset of the
+    // tile's record in d_pack in 16-byte units, bit 31 set when the record is a dense 4 KB tile; d_rec[tilenum] = end.
+    void *d_bitmap = nullptr;
+    unsigned int *d_rec = nullptr;
+    unsigned char *d_pack = nullptr;
+    long long pack_bytes = 0;
     std::vector<int> h_tile_ptr, h_panel_row;
     // schedule for the current threshold
     int TH = 0, ntasks = 0, nsplit = 0;
@@ -124,6 +136,12 @@ struct tsp_handle
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     long long launches = 0;
     int *d_error = nullptr;           // device-side error flag (bounded waits)
+    // all tile arrays of the three classes live in two allocations (the second holds the packed 64-row records)
+    void *tile_block = nullptr, *pack_block = nullptr;
+    // conversion workspace: chunks of device memory reused by every conversion of this handle, and a small pinned
+    // host buffer for the few scalars a conversion reads back
+    std::vector<std::pair<void *, size_t>> ws_chunks;
+    void *h_pin = nullptr;
     // device staging of the host-buffer entry points: two slots, so that the upload of one call overlaps the
     // download of the previous one (PCIe is full duplex); one stream per direction plus a compute stream
     void *stage_b[2] = {nullptr, nullptr};
@@ -140,10 +158,15 @@ struct tsp_handle
 
 // ---------------------------------------------------------------- cross-TU entry points
 
-int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz, const int *d_rowptr, const int *d_colidx,
-                     const void *d_val, float gamma, float delta, int shard_index, int shard_count);
+// rowptr/colidx/val are device pointers, or host pointers when csr_on_host (uploaded into the conversion workspace)
+int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz, const int *rowptr, const int *colidx, const void *val,
+                     bool csr_on_host, float gamma, float delta, int shard_index, int shard_count);
 void tsp_free_tiles(tsp_handle *h);
 int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst);
+// one allocation for the tile arrays of all classes (sizes from cls[k].tilem / tilenum), zero-filled where needed
+int tsp_alloc_tile_arrays(tsp_handle *h);
+int tsp_alloc_pack(tsp_handle *h, long long bytes);
+void tsp_free_workspace(tsp_handle *h);
 
 // class kernels; C is addressed relative to row_begin.  count_only != 0 skips the launch and only reports
 // how many launches the call would make.
@@ -153,4 +176,5 @@ int tsp_launch_small(tsp_handle *h, int cls, const void *d_b, float *d_c, int co
 int tsp_launch_small_t(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB, cudaStream_t s);
 bool tsp_small_t_supported(int colB);
 int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
+int tsp_launch_selftest_wait(tsp_handle *h, unsigned polls, cudaStream_t s);
 void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);

@@ -26,7 +26,10 @@ import time
 
 import numpy as np
 
-from .sweep_thresholds import ALL as CANDIDATES   # upstream's order: index = leaf number
+# upstream's candidate table in upstream's order (src/model.h:14-38): index = leaf number
+GAMMAS = [1.0, 1.4, 1.8, 2.0, 2.4, 2.8, 3.0, 3.4, 3.8, 4.0]
+DELTAS = [1.0, 1.2, 1.4, 1.5, 1.8, 2.0]
+CANDIDATES = [(0.0, 1.5), (5.0, 0.0), (5.0, 3.0)] + [(g, d) for g in GAMMAS for d in DELTAS] + [(2.5, 1.0), (2.5, 1.2), (3.5, 1.0)]
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 TABLE = os.path.join(HERE, "csrc", "model_table.inc")
