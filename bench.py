@@ -386,7 +386,7 @@ def measure(name: str, cx, headline: bool):
     ew1.record()
     barrier()
     est_ms = multi.max_over_ranks(max(ew0.elapsed_time(ew1) / args.warmup, 1e-3), dist, "cuda")
-    min_s = MIN_TIMED_S if headline else 0.4
+    min_s = args.min_seconds if headline else min(0.4, args.min_seconds)
     repeats = int(min(max(5, math.ceil(min_s * 1e3 / (est_ms * K))), 5000))
     launches0 = m.launch_count()
     sampler = ClockSampler(local) if (headline and rank == 0) else None
@@ -533,6 +533,8 @@ def main():
     ap.add_argument("--no-upstream", action="store_true", help="skip the leg that runs upstream's own kernels")
     ap.add_argument("--no-per-config", action="store_true", help="headline workload only")
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_S,
+                    help="shortest total length of the timed loops of the headline workload (0: five loops; for profiling runs)")
     ap.add_argument("--th", default=None, help="th64,th16,th8: fixed thresholds, skips the on-GPU tuning (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

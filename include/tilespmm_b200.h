@@ -68,7 +68,7 @@ int tsp_convert_device(tsp_handle *h, int rowA, int colA, long long nnz, const i
                        const void *d_val, float gamma, float delta, int shard_index, int shard_count);
 
 /* info12[c*4 + {0,1,2,3}] = rows, nnz, panels (tilem), tiles (tilenum) of class c -- the quantities upstream
- * prints into its CSV row (src/main.cu:306-307).  shard_rows[2] = first and one-past-last original row of
+ * prints into its CSV row (src/main.cu:306-307); all fit an int because the whole matrix is limited to 2^31-1 entries.  shard_rows[2] = first and one-past-last original row of
  * the C slab this handle writes. */
 int tsp_info(const tsp_handle *h, int *info12, int *shard_rows2);
 
@@ -78,8 +78,9 @@ int tsp_info(const tsp_handle *h, int *info12, int *shard_rows2);
  * 5 orig_tile_row_idx[tilem].  Arrays with no upstream counterpart, 64-row class only (cls 0): 6 the row masks,
  * [tilenum][64] words of 16 bits (TF32) or 32 bits (FP16), bit k of word r set when position (r, k) of the tile holds
  * a stored entry (an explicit zero counts); 7 rec[tilenum+1], offset of every tile's record in 16-byte units with bit
- * 31 set for a dense record; 8 the records: a packed record is the 64 masks followed by the values of the set
- * positions in row-major order (padded to 16 bytes), a dense record (more than 128 TF32 / 256 FP16 values) is the
+ * 31 set for a dense record; 8 the records: a packed record of a tile with n entries is n rounded up to 8 positions
+ * of 16 bits (the entry's element index in the 4 KB tcgen05 operand tile, 0xffff in the padding) followed by as many
+ * values, both in row-major order of the set mask bits; a dense record (more than 128 TF32 / 256 FP16 entries) is the
  * 4 KB tile in tcgen05 core-matrix order.  h_dst == NULL only queries the size.  *bytes receives the size. */
 int tsp_export(const tsp_handle *h, int cls, int which, void *h_dst, long long *bytes);
 
@@ -96,11 +97,13 @@ int tsp_schedule(tsp_handle *h, int cls, int TH);
 /* No counterpart in upstream.  The same task arrays as tsp_schedule(), built without cudaMalloc/cudaFree or
  * any allocating library call, for hosts that own all device memory themselves (a pre-carved arena) or may
  * not enter the allocator on their hot path.  The per-panel counters live in a fixed device array inside
- * the library (4 MB per GPU, held until the process exits), so tilem is limited to 1,048,576 panels
+ * the library (4 MB + 260 bytes per GPU, held until the process exits), so tilem is limited to 1,048,576 panels
  * (TSP_EINVAL beyond that).  Inputs d_tile_ptr[tilem+1], d_panel_row[tilem]; outputs d_task_row[capacity],
  * d_task_start[capacity+1], d_split_row[tilem] (may be NULL) are caller-owned device arrays; *ntasks and
  * *nsplit are host outputs.  TSP_ENOMEM (with *ntasks = tasks needed, nothing written) when capacity is too
- * small.  The first call on a device resolves the array's device address: make it before any stream capture.
+ * small.  The first call on a device resolves the array's device address and loads the kernels (both may allocate
+ * inside the CUDA runtime): make it at start-up, before any stream capture and before the arena is carved.  The
+ * caller's current device is restored on return.
  * Calls share the array: back-to-back calls are fine, calls that can overlap on one GPU race.  Waits for
  * `stream` before returning. */
 int tsp_schedule_noalloc(int device, int tilem, int TH, const int *d_tile_ptr, const int *d_panel_row,
@@ -156,6 +159,27 @@ int tsp_time(tsp_handle *h, int cls, const void *d_b, float *d_c, int colB_padde
  * time_ms, tflops = 2*nnz*colB_logical/time}. */
 int tsp_run(tsp_handle *h, const void *h_b, float *h_c, int colB_padded, int colB_logical, double cpu_pre_time_ms,
             int repeat, double *out6);
+
+/* ---- several GPUs of one box inside one process (no upstream counterpart: upstream runs on the one GPU `-d` names,
+ * src/main.cu:138-142, 210).  The panel sequence of the matrix is cut into contiguous ranges balanced by tile bytes, one
+ * per device; every device converts and multiplies its range and owns the matching row slab of C.  B is uploaded in N
+ * row blocks, one per device, and all-gathered over NCCL (loaded at run time; not needed for one device) into every
+ * device's own memory; C is row-partitioned, no reduction.  The calls mirror the single-GPU ones above. */
+typedef struct tsp_multi tsp_multi;
+int tsp_multi_create(tsp_multi **out, int ndev, const int *devices, int precision);
+int tsp_multi_destroy(tsp_multi *m);
+int tsp_multi_device_count(const tsp_multi *m);
+/* one host thread per device converts that device's shard (tsp_convert_host with shard i of ndev) */
+int tsp_multi_convert_host(tsp_multi *m, int rowA, int colA, long long nnz, const int *h_rowptr, const int *h_colidx,
+                           const void *h_val, float gamma, float delta);
+/* info12 as tsp_info, summed over the devices; slabs2n[2i], slabs2n[2i+1] = rows of device i's slab of C (may be NULL) */
+int tsp_multi_info(const tsp_multi *m, int *info12, int *slabs2n);
+/* h_b: colA x colB_padded values; h_c: rowA x colB_padded floats */
+int tsp_multi_spmm_host(tsp_multi *m, const void *h_b, float *h_c, int colB_padded);
+/* tsp_run over the devices: per-device tuning, checked product (h_c may be NULL), `repeat` timed passes on all devices
+ * together; out6 as tsp_run with the thresholds of device 0 and the slowest device's mean time */
+int tsp_multi_run(tsp_multi *m, const void *h_b, float *h_c, int colB_padded, int colB_logical, double cpu_pre_time_ms,
+                  int repeat, double *out6);
 
 /* ---- the cuSPARSE baseline upstream runs next to its own kernels, cusparse_spmm_all (src/main.cu:16-134):
  * CSR, CUSPARSE_SPMM_ALG_DEFAULT, FP32 compute; FP16 inputs for precision 0 and true FP32 inputs for

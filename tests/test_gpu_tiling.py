@@ -196,30 +196,32 @@ def masks_from_csr(prec, shape, rp, ci, o):
 
 
 def dense_from_records(prec, masks, rec, records):
-    """Upstream's dense 64-row tiles rebuilt on the CPU from the exported records (not through the library's own export)."""
+    """Upstream's dense 64-row tiles rebuilt on the CPU from the exported records (not through the library's own export).
+    A packed record: n_pad = n rounded up to 8 positions (uint16, the element's index in the tcgen05 operand tile, 0xffff
+    in the padding), then n_pad values, both in row-major order of the set mask bits.  A dense record: the 4 KB tile."""
     bn, vt = _orc.BN(prec, 0), (np.uint16 if prec == 0 else np.float32)
-    vsz, mb = (2 if prec == 0 else 4), (256 if prec == 0 else 128)
+    vsz = 2 if prec == 0 else 4
     ntile = masks.shape[0]
     out = np.zeros((ntile, 64 * bn), dtype=vt)
     r_idx, k_idx = np.meshgrid(np.arange(64), np.arange(bn), indexing="ij")
     up = _upstream64(prec, r_idx, k_idx)
     um = _umma64(prec, r_idx, k_idx)
     for t in range(ntile):
-        off = int(rec[t] & 0x7fffffff) * 16
-        if rec[t] >> 31:
-            tile = records[off:off + 4096].view(vt)
-            out[t, up.ravel()] = tile[um.ravel()]
-            assert int(rec[t + 1] & 0x7fffffff) * 16 - off == 4096
-            continue
-        stored = records[off:off + mb].view(np.uint32 if prec == 0 else np.uint16)
-        assert np.array_equal(stored.astype(np.uint32), masks[t])             # the record starts with the tile's masks
+        off, end = int(rec[t] & 0x7fffffff) * 16, int(rec[t + 1] & 0x7fffffff) * 16
         set_bits = ((masks[t][:, None] >> np.arange(bn, dtype=np.uint32)[None, :]) & 1).astype(bool)   # [64, bn], row-major
         n = int(set_bits.sum())
-        assert n <= (256 if prec == 0 else 128)
-        assert int(rec[t + 1] & 0x7fffffff) * 16 - off == mb + (n * vsz + 15) // 16 * 16
-        vals = records[off + mb:off + mb + n * vsz].view(vt)
-        out[t, up[set_bits]] = vals
-        assert not records[off + mb + n * vsz:int(rec[t + 1] & 0x7fffffff) * 16].any()   # padding is zero
+        if rec[t] >> 31:
+            assert end - off == 4096 and n > (256 if prec == 0 else 128)
+            tile = records[off:off + 4096].view(vt)
+            out[t, up.ravel()] = tile[um.ravel()]
+            continue
+        n_pad = (n + 7) // 8 * 8
+        assert n <= (256 if prec == 0 else 128) and end - off == n_pad * (2 + vsz)
+        pos = records[off:off + 2 * n_pad].view(np.uint16)
+        vals = records[off + 2 * n_pad:end].view(vt)
+        np.testing.assert_array_equal(pos[:n], um[set_bits])                 # positions follow the masks, row-major
+        assert (pos[n:] == 0xffff).all() and not vals[n:].any()               # padding
+        out[t, up[set_bits]] = vals[:n]
     return out.ravel()
 
 

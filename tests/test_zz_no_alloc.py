@@ -16,9 +16,12 @@ def _noalloc(L, tile_ptr_d, panel_row_d, tilem, TH, capacity, torch):
     start = torch.full((max(capacity, 1) + 1,), -1, dtype=torch.int32, device="cuda")
     split = torch.zeros(max(tilem, 1), dtype=torch.int32, device="cuda")
     n, ns = C.c_int(-1), C.c_int(-1)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]                    # cudaMemGetInfo: what the driver has left on the device
     rc = L.tsp_schedule_noalloc(0, tilem, TH, C.c_void_p(tile_ptr_d.data_ptr()), C.c_void_p(panel_row_d.data_ptr()),
                                 C.c_void_p(rows.data_ptr()), C.c_void_p(start.data_ptr()), C.c_longlong(capacity),
                                 C.c_void_p(split.data_ptr()), C.byref(n), C.byref(ns), None)
+    _noalloc.device_bytes_taken = free_before - torch.cuda.mem_get_info()[0]
     return rc, n.value, ns.value, rows, start, split
 
 
@@ -31,6 +34,7 @@ def test_noalloc_schedule_equals_allocating_schedule_twice_in_a_row():
     rp, ci, v, shape = synth.rmat_symmetric(13, 16, 4242)        # skewed rows: many split panels at small TH
     m = api.TileMatrix(0).convert_host(shape, rp, ci, v, 2.0, 1.2)
     info = m.info()
+    calls = 0
     for cls in range(3):
         tilem = int(info[cls, 2])
         if tilem == 0:
@@ -42,6 +46,9 @@ def test_noalloc_schedule_equals_allocating_schedule_twice_in_a_row():
             cap = int(want_rows.size) + 5
             rc, n, ns, rows, start, split = _noalloc(L, tile_ptr_d, panel_row_d, tilem, TH, cap, torch)
             assert rc == 0, L.tsp_last_error()
+            calls += 1
+            if calls > 1:      # the first call on a device may load the kernels; every later one takes no device memory at all
+                assert _noalloc.device_bytes_taken == 0, _noalloc.device_bytes_taken
             assert n == want_rows.size
             np.testing.assert_array_equal(rows[:n].cpu().numpy().view(np.uint32), want_rows)
             np.testing.assert_array_equal(start[:n + 1].cpu().numpy(), want_start)

@@ -253,3 +253,58 @@ def cusparse_baseline(precision, shape, rowptr, colidx, vals, h_b, colB, device=
         _check(lib().tsp_cusparse_baseline(device, precision, shape[0], shape[1], colidx.size, _p(rowptr), _p(colidx), _p(v),
                                            colB, h_b.shape[1], _p(h_b), _p(c), warmup, repeat, _p(out3)), "tsp_cusparse_baseline")
     return out3, c
+
+
+class MultiTileMatrix:
+    """One matrix spread over several GPUs of this box inside one process (the tsp_multi_* layer of the C ABI): every
+    device converts and multiplies a contiguous range of panels and owns the matching row slab of C; B is uploaded in
+    row blocks and all-gathered over NCCL."""
+
+    def __init__(self, precision: int, devices):
+        self.L = lib()
+        vp, i, ll, f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+        self.L.tsp_multi_create.argtypes = [C.POINTER(vp), i, vp, i]
+        self.L.tsp_multi_destroy.argtypes = [vp]
+        self.L.tsp_multi_convert_host.argtypes = [vp, i, i, ll, vp, vp, vp, f, f]
+        self.L.tsp_multi_info.argtypes = [vp, vp, vp]
+        self.L.tsp_multi_spmm_host.argtypes = [vp, vp, vp, i]
+        self.L.tsp_multi_run.argtypes = [vp, vp, vp, i, i, C.c_double, i, vp]
+        self.precision = precision
+        self.devices = np.ascontiguousarray(devices, dtype=np.int32)
+        self.h = C.c_void_p()
+        _check(self.L.tsp_multi_create(C.byref(self.h), int(self.devices.size), _p(self.devices), precision), "tsp_multi_create")
+        self.shape = None
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.tsp_multi_destroy(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def convert_host(self, shape, rowptr, colidx, vals, gamma, delta):
+        rowptr = np.ascontiguousarray(rowptr, np.int32)
+        colidx = np.ascontiguousarray(colidx, np.int32)
+        v = vals if (isinstance(vals, np.ndarray) and vals.dtype == np.uint16) else to_values(vals, self.precision)
+        self.shape = tuple(shape)
+        _check(self.L.tsp_multi_convert_host(self.h, shape[0], shape[1], colidx.size, _p(rowptr), _p(colidx), _p(v), gamma, delta),
+               "tsp_multi_convert_host")
+        return self
+
+    def info(self):
+        out = np.zeros(12, dtype=np.int32)
+        slabs = np.zeros(2 * self.devices.size, dtype=np.int32)
+        _check(self.L.tsp_multi_info(self.h, _p(out), _p(slabs)), "tsp_multi_info")
+        self.slabs = [tuple(int(x) for x in slabs[2 * k:2 * k + 2]) for k in range(self.devices.size)]
+        return out.reshape(3, 4)
+
+    def spmm_host(self, h_b: np.ndarray, colB_padded: int) -> np.ndarray:
+        out = np.zeros((self.shape[0], colB_padded), dtype=np.float32)
+        _check(self.L.tsp_multi_spmm_host(self.h, _p(h_b), _p(out), colB_padded), "tsp_multi_spmm_host")
+        return out
+
+    def run(self, h_b: np.ndarray, colB_padded: int, colB_logical: int, repeat: int = 1000):
+        out6 = np.zeros(6, dtype=np.float64)
+        c = np.zeros((self.shape[0], colB_padded), dtype=np.float32)
+        _check(self.L.tsp_multi_run(self.h, _p(h_b), _p(c), colB_padded, colB_logical, 0.0, repeat, _p(out6)), "tsp_multi_run")
+        return out6, c

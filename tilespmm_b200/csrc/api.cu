@@ -288,6 +288,12 @@ static int check_device_error(tsp_handle *h)
     if (flag)
     {
         cudaMemset(h->d_error, 0, 4);
+        if (flag >= 0x20 && flag <= 0x22)   // only the checked build (-DTSP_DEBUG) produces these
+        {
+            tsp_set_error("checked build: %s (code 0x%x); the access was skipped and the result of that launch is incomplete",
+                          flag == 0x20 ? "a tile names a column outside B" : (flag == 0x21 ? "a task lies outside the class's tiles" : "a task writes rows outside C"), flag);
+            return TSP_EINVAL;
+        }
         tsp_set_error("a bounded wait inside an SpMM kernel ran out (code 0x%x); the result of that launch is incomplete", flag);
         return TSP_ETIMEOUT;
     }
@@ -304,6 +310,30 @@ extern "C" int tsp_check_error(tsp_handle *h, void *stream)
     else TSP_CUDA(cudaDeviceSynchronize());
     return check_device_error(h);
 }
+
+#ifdef TSP_DEBUG
+// Checked build only (libtilespmm_b200_debug.so): overwrites one index on the device so that the kernels' own checks can
+// be exercised -- what 0: tile_colidx[index] of class cls, 1: the end tile of task `index` of class cls.  The release
+// library does not have this entry point; its kernels never see a damaged index from this library's own conversion.
+extern "C" int tsp_debug_poke(tsp_handle *h, int cls, int what, long long index, int value)
+{
+    if (!h || cls < 0 || cls > 2 || !h->converted || index < 0) { tsp_set_error("debug_poke: bad argument"); return TSP_EINVAL; }
+    TSP_CUDA(cudaSetDevice(h->device));
+    TspClass &c = h->cls[cls];
+    if (what == 0)
+    {
+        if (index >= (long long)c.tilenum * c.BN) { tsp_set_error("debug_poke: index outside tile_colidx"); return TSP_EINVAL; }
+        TSP_CUDA(cudaMemcpy(c.d_tile_colidx + index, &value, 4, cudaMemcpyHostToDevice));
+    }
+    else
+    {
+        if (index >= c.ntasks) { tsp_set_error("debug_poke: index outside the task list (schedule first)"); return TSP_EINVAL; }
+        if (cls == 0) TSP_CUDA(cudaMemcpy(c.d_task_start + index + 1, &value, 4, cudaMemcpyHostToDevice));
+        else TSP_CUDA(cudaMemcpy(&c.d_task_pack[index].z, &value, 4, cudaMemcpyHostToDevice));
+    }
+    return TSP_OK;
+}
+#endif
 
 extern "C" int tsp_selftest_wait_timeout(tsp_handle *h, int polls)
 {

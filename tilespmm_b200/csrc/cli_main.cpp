@@ -1,10 +1,12 @@
-// tilespmm_fp16 / tilespmm_tf32 -d <device_id> <matrix.mtx> <colB>
+// tilespmm_fp16 / tilespmm_tf32 -d <device_id> <matrix.mtx> <colB> [--gpus N]
 //
 // Drop-in for the two upstream executables (src/main.cu:136-352): same arguments and exit codes, the same
 // synthetic inputs (srand(1325), values 1 + rand() % 3 in CSR order, then B, src/main.cu:177-207), the same 19-field
 // CSV row without header appended to TileSpMM-FP16.csv / TileSpMM-TF32.csv in the working directory
 // (src/main.cu:293-308, src/csr2tile.h:1062, src/main.cu:82,115), the same check against cuSPARSE at 1e-3 absolute
 // (src/main.cu:315-335).  Everything on the GPU goes through the C ABI of libtilespmm_b200.so.
+// Opt-in extension, absent upstream: a trailing `--gpus N` spreads the panels of A over the devices device_id ..
+// device_id+N-1 (tsp_multi_*); the CSV row keeps its 19 fields (thresholds of the first device, time of the slowest).
 // Built once per precision with -DTSP_PRECISION=0 (FP16) or 1 (TF32).
 #include <cuda_runtime.h>
 #include <limits.h>
@@ -74,6 +76,10 @@ int main(int argc, char **argv)
         printf("Usage: %s -d device_id matrix.mtx colB\n", argv[0]);
         return EXIT_FAILURE;
     }
+    int gpus = 1;
+    for (int a = 5; a + 1 < argc; a++)
+        if (strcmp(argv[a], "--gpus") == 0) gpus = atoi(argv[a + 1]);
+    if (gpus < 1 || gpus > 64) { fprintf(stderr, "--gpus must be between 1 and 64.\n"); return EXIT_FAILURE; }
     printf("--------------------------------!!!!!!!!------------------------------------\n");
     const int device_id = atoi(argv[2]);
     printf("device_id = %i\n", device_id);
@@ -128,7 +134,15 @@ int main(int argc, char **argv)
     printf("  Device [ %i ] %s @ %4.2f MHz\n", device_id, prop.name, clock_khz * 1e-3f);
 
     tsp_handle *h = NULL;
-    FAIL_IF(tsp_create(&h, device_id, TSP_PRECISION), "create");
+    tsp_multi *mg = NULL;
+    if (gpus > 1)
+    {
+        int devices[64];
+        for (int i = 0; i < gpus; i++) devices[i] = device_id + i;
+        FAIL_IF(tsp_multi_create(&mg, gpus, devices, TSP_PRECISION), "create");
+        printf("  panels of A spread over %d devices (%d..%d)\n", gpus, device_id, device_id + gpus - 1);
+    }
+    else FAIL_IF(tsp_create(&h, device_id, TSP_PRECISION), "create");
     t1 = wall_ms();
     double features[11];
     const double capability = prop.major + prop.minor / 10.0;
@@ -139,11 +153,12 @@ int main(int argc, char **argv)
     }
     float gamma = 0.0f, delta = 0.0f;
     if (TSP_PRECISION) tilespmm_predict_tf32(features, &gamma, &delta); else tilespmm_predict_fp16(features, &gamma, &delta);
-    FAIL_IF(tsp_convert_host(h, rowA, colA, nnzA, rowptr, colidx, valA, gamma, delta, 0, 1), "convert");
+    if (mg) FAIL_IF(tsp_multi_convert_host(mg, rowA, colA, nnzA, rowptr, colidx, valA, gamma, delta), "convert");
+    else FAIL_IF(tsp_convert_host(h, rowA, colA, nnzA, rowptr, colidx, valA, gamma, delta, 0, 1), "convert");
     const double pre_time = wall_ms() - t1;
     printf("  CPU preprocessing time = %4.5f s\n", pre_time / 1000.0);
     int info[12];
-    tsp_info(h, info, NULL);
+    if (mg) tsp_multi_info(mg, info, NULL); else tsp_info(h, info, NULL);
 
     const char *csv_path = TSP_PRECISION ? "TileSpMM-TF32.csv" : "TileSpMM-FP16.csv";
     FILE *fout = fopen(csv_path, "a");
@@ -155,7 +170,8 @@ int main(int argc, char **argv)
     float *matrixC_cusparse = (float *)malloc(sizeof(float) * (size_t)rowA * colB);
     if (!matrixC || !matrixC_cusparse) { fprintf(stderr, "Host memory allocation failed\n"); return EXIT_FAILURE; }
     double out6[6], out3[3];
-    FAIL_IF(tsp_run(h, matrixB, matrixC, colB_padded, colB, pre_time, BENCH_REPEAT, out6), "run");
+    if (mg) FAIL_IF(tsp_multi_run(mg, matrixB, matrixC, colB_padded, colB, pre_time, BENCH_REPEAT, out6), "run");
+    else FAIL_IF(tsp_run(h, matrixB, matrixC, colB_padded, colB, pre_time, BENCH_REPEAT, out6), "run");
     printf("  TileSpMM runtime %4.3f ms, %4.3f TFlops\n", out6[4], out6[5]);
     fprintf(fout, "%d,%d,%d,%.9g,%.9g,%.9g,", (int)out6[0], (int)out6[1], (int)out6[2], out6[3], out6[4], out6[5]);
     fflush(fout);
@@ -183,6 +199,7 @@ int main(int argc, char **argv)
     else printf("  Check... NO PASS! error_count_cuda = %zu\n", errors);
     fclose(fout);
     tsp_destroy(h);
+    tsp_multi_destroy(mg);
     free(matrixC); free(matrixC_cusparse); free(matrixB); free(valA);
     tsp_free_host(rowptr); tsp_free_host(colidx);
     return EXIT_SUCCESS;

@@ -508,7 +508,7 @@ __global__ void k_rec_sizes(int tilenum, int precision, const unsigned int *__re
 {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
-    const int vsz = precision ? 4 : 2, max_vals = TSP_REC_MAX_VALS(precision), mask_bytes = tsp_mask_bytes(precision);
+    const int vsz = precision ? 4 : 2, max_vals = TSP_REC_MAX_VALS(precision);
     for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tilenum; t += warps)
     {
         // lane l owns rows 2l and 2l+1
@@ -525,7 +525,7 @@ __global__ void k_rec_sizes(int tilenum, int precision, const unsigned int *__re
         {
             const bool is_dense = total > max_vals;
             dense[t] = is_dense ? 1 : 0;
-            units[t] = is_dense ? (64u * tsp_bn(precision, 0) * vsz) / 16u : (unsigned int)(mask_bytes + ((total * vsz + 15) & ~15)) / 16u;
+            units[t] = is_dense ? (64u * tsp_bn(precision, 0) * vsz) / 16u : tsp_packed_units(precision, total);
         }
     }
 }
@@ -540,32 +540,33 @@ __global__ void k_rec_finish(int tilenum, const unsigned int *__restrict__ prefi
     rec[t] = prefix[t] | (t < tilenum && dense[t] ? 0x80000000u : 0u);
 }
 
-// Row masks into the head of every packed record.
-__global__ void k_copy_masks(int tilenum, int precision, const unsigned int *__restrict__ mask64, const unsigned int *__restrict__ rec,
-                             unsigned char *__restrict__ pack)
+// The position slots of every packed record start as 0xffff ("no entry"); the padding keeps that value.
+__global__ void k_init_positions(int tilenum, int precision, const unsigned int *__restrict__ rec, unsigned char *__restrict__ pack)
 {
-    const int words = tsp_mask_bytes(precision) / 4;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)tilenum * words; i += (long long)gridDim.x * blockDim.x)
+    const int per = 2 + (precision ? 4 : 2);
+    for (int t = blockIdx.x; t < tilenum; t += gridDim.x)
     {
-        const int t = (int)(i / words), w = (int)(i - (long long)t * words);
         const unsigned int r = rec[t];
         if (r >> 31) continue;
-        reinterpret_cast<unsigned int *>(pack + (size_t)r * 16)[w] = mask64[i];
+        const unsigned int n_pad = ((rec[t + 1] & 0x7fffffffu) - r) * 16u / per;
+        unsigned short *posn = reinterpret_cast<unsigned short *>(pack + (size_t)r * 16);
+        for (unsigned int i = threadIdx.x; i < n_pad; i += blockDim.x) posn[i] = 0xffffu;
     }
 }
 
-// One warp per original row of the 64-row class: every entry's value goes to its place in the tile's record -- the
-// position given by the masks for a packed record, the operand position for a dense one.
+// One warp per original row of the 64-row class: every entry's value goes to its place in the tile's record -- for a
+// packed record the slot given by the masks (row-major order of the set bits), together with the entry's position in
+// the operand tile; for a dense record the operand position itself.
 template <typename V>
 __global__ void k_place_values64(int rowA, int precision, int s0, int s1, const int *__restrict__ rowptr, const int *__restrict__ colidx,
                                  const V *__restrict__ val, const int *__restrict__ blk_seq, const unsigned char *__restrict__ seq_cls,
                                  const int *__restrict__ seq_idx, const int *__restrict__ seq_blk, const int *__restrict__ pptr,
                                  const int *__restrict__ pcols, int p0_64, const int *__restrict__ tp64, const unsigned int *__restrict__ mask64,
-                                 const unsigned short *__restrict__ row_off, const unsigned int *__restrict__ rec, V *__restrict__ pack)
+                                 const unsigned short *__restrict__ row_off, const unsigned int *__restrict__ rec, V *pack)
 {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
-    const int bn = tsp_bn(precision, 0), mask_elems = tsp_mask_bytes(precision) / (int)sizeof(V), per16 = 16 / (int)sizeof(V);
+    const int bn = tsp_bn(precision, 0), per16 = 16 / (int)sizeof(V), per = 2 + (int)sizeof(V);
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rowA; r += warps)
     {
         const int s = blk_seq[r >> 3];
@@ -593,7 +594,11 @@ __global__ void k_place_values64(int rowA, int precision, int s0, int s1, const 
                     const size_t bit = ((size_t)t * 64 + ri) * bn;          // first bit of the row mask
                     unsigned int m = mask64[bit >> 5] >> (bit & 31);
                     if (precision) m &= 0xffffu;
-                    pos = rec_elem + mask_elems + row_off[(size_t)t * 64 + ri] + __popc(m & ((1u << c) - 1u));
+                    const unsigned int n_pad = ((rec[t + 1] & 0x7fffffffu) - rw) * 16u / per;
+                    const unsigned int slot = row_off[(size_t)t * 64 + ri] + __popc(m & ((1u << c) - 1u));
+                    // positions first (2 bytes each), then the values: n_pad * 2 bytes is a multiple of 16
+                    pos = rec_elem + (unsigned long long)(n_pad * 2u / sizeof(V)) + slot;
+                    reinterpret_cast<unsigned short *>(pack + (size_t)rw * per16)[slot] = (unsigned short)tsp_umma_index(precision, ri, c);
                 }
                 v = val[j];
             }
@@ -610,7 +615,7 @@ __global__ void k_export64(int tilenum, int precision, const unsigned int *__res
 {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
-    const int bn = tsp_bn(precision, 0), per = 64 * bn, mask_bytes = tsp_mask_bytes(precision);
+    const int bn = tsp_bn(precision, 0), per = 64 * bn;
     for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tilenum; t += warps)
     {
         const unsigned int rw = rec[t];
@@ -622,18 +627,17 @@ __global__ void k_export64(int tilenum, int precision, const unsigned int *__res
             for (int e = lane; e < per; e += 32) { const int r = e / bn, c = e - r * bn; out[tsp_upstream_index(precision, 0, r, c)] = src[tsp_umma_index(precision, r, c)]; }
             continue;
         }
-        unsigned int w0, w1;
-        const unsigned int *masks = reinterpret_cast<const unsigned int *>(record);
-        if (precision) { const unsigned int w = masks[lane]; w0 = w & 0xffffu; w1 = w >> 16; }
-        else { w0 = masks[2 * lane]; w1 = masks[2 * lane + 1]; }
-        const int cnt = __popc(w0) + __popc(w1);
-        int incl = cnt;
-        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
-        const V *src = reinterpret_cast<const V *>(record + mask_bytes) + (incl - cnt);
-        for (int half = 0; half < 2; half++)
+        // packed: positions (operand order) and values; the inverse of tsp_umma_index gives (row, column)
+        const int per_rec = 2 + (int)sizeof(V), T = 16 / (int)sizeof(V);
+        const unsigned int n_pad = ((rec[t + 1] & 0x7fffffffu) - rw) * 16u / per_rec;
+        const unsigned short *posn = reinterpret_cast<const unsigned short *>(record);
+        const V *src = reinterpret_cast<const V *>(record + n_pad * 2);
+        for (unsigned int i = lane; i < n_pad; i += 32)
         {
-            unsigned int w = half ? w1 : w0;
-            while (w) { const int c = __ffs(w) - 1; w &= w - 1; out[tsp_upstream_index(precision, 0, 2 * lane + half, c)] = *src++; }
+            const unsigned int u = posn[i];
+            if (u == 0xffffu) continue;
+            const int core = u / (8 * T), r = ((core & 7) << 3) + (u % (8 * T)) / T, c = (core >> 3) * T + u % T;
+            out[tsp_upstream_index(precision, 0, r, c)] = src[i];
         }
     }
 }
@@ -802,6 +806,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         return TSP_EINVAL;
     }
     TSP_CUDA(cudaSetDevice(h->device));
+    TspRange range_all("tsp convert");
     tsp_free_tiles(h);
     h->rowA = rowA; h->colA = colA; h->nnzA = nnz64;
     const int nnz = (int)nnz64;
@@ -860,6 +865,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     TSP_CUDA(cudaMemsetAsync(class_rows_nnz, 0, 6 * sizeof(unsigned long long), st));
 
     // ---- stage 1: sorted distinct columns of every 8-row block
+    nvtxRangePushA("tsp convert: partition (stages 1-3)");
     {
         const int blocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
         k_make_block_keys<<<blocks, T, 0, st>>>(rowA, colA, nnz, d_rowptr, d_colidx, keys, d_bad);   // also checks the row pointers of an empty matrix
@@ -889,6 +895,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     TSP_CUDA(cudaMemcpyAsync(pin + 2, base + (size_t)nchunk * 3, 3 * sizeof(int), cudaMemcpyDeviceToHost, st));
     TSP_CUDA(cudaMemcpyAsync(pin + 8, class_rows_nnz, 6 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
     TSP_CUDA(cudaStreamSynchronize(st));
+    nvtxRangePop();
     const int nu = pin[0];
     if (pin[1])
     {
@@ -901,6 +908,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     const int nseq = totals[0] + totals[1] + totals[2];
 
     // ---- stage 4: sorted distinct columns of every panel
+    TspRange range_tiles("tsp convert: tiles (stages 4-6)");
     const int *pptr = nullptr, *pcols = nullptr;
     const bool all8 = totals[0] == 0 && totals[1] == 0;
     if (all8) { pptr = u8_ptr; pcols = ucols; }  // an 8-row panel is one 8-row block
@@ -1056,8 +1064,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
             const long long total_units = (unsigned int)pin[0];
             if (total_units >= 0x7fffffffLL) { tsp_set_error("convert: the 64-row tile records exceed 32 GB"); return TSP_EINVAL; }
             TSP_TRY(tsp_alloc_pack(h, total_units * 16));
-            k_copy_masks<<<blocks_for((long long)c.tilenum * 32, T) > 148 * 16 ? 148 * 16 : blocks_for((long long)c.tilenum * 32, T), T, 0, st>>>(
-                c.tilenum, prec, (const unsigned int *)c.d_bitmap, c.d_rec, c.d_pack);
+            k_init_positions<<<c.tilenum > 148 * 16 ? 148 * 16 : c.tilenum, 64, 0, st>>>(c.tilenum, prec, c.d_rec, c.d_pack);
             const int vblocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
             if (prec == 0)
                 k_place_values64<__half><<<vblocks, T, 0, st>>>(rowA, 0, s0, s1, d_rowptr, d_colidx, (const __half *)d_val, blk_seq, seq_cls, seq_idx,

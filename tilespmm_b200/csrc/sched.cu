@@ -8,6 +8,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "tsp_internal.cuh"
 
 void tsp_small_resources(int precision, int cls, int colB, TspKernelResources *out);
@@ -118,6 +120,7 @@ int tsp_schedule(tsp_handle *h, int cls, int TH)
     if (!h || cls < 0 || cls > 2 || TH <= 0) { tsp_set_error("schedule: bad argument"); return TSP_EINVAL; }
     if (!h->converted) { tsp_set_error("schedule: convert first"); return TSP_ESTATE; }
     TSP_CUDA(cudaSetDevice(h->device));
+    TspRange range("tsp schedule");
     TspClass &c = h->cls[cls];
     c.TH = TH; c.ntasks = 0; c.nsplit = 0;
     if (c.tilem == 0) return TSP_OK;
@@ -278,7 +281,7 @@ int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
 // cudaMalloc/cudaFree would stall the whole device on its hot path), or a real-time loop that is not allowed
 // to enter the allocator at all.  For them tsp_schedule_noalloc() does the same work with the per-panel
 // counters kept in the fixed device array below, which every GPU that loads this library holds until the
-// process exits (4 MB + 256 B).  The caller provides the tile pointers, the panel rows and the output arrays.
+// process exits (4 MB + 260 B).  The caller provides the tile pointers, the panel rows and the output arrays.
 // ---------------------------------------------------------------------------------------------------------
 
 #define TSP_NOALLOC_MAX_PANELS (1 << 20)
@@ -290,8 +293,10 @@ static __device__ __align__(256) int g_noalloc_scratch[TSP_NOALLOC_MAX_PANELS + 
 namespace
 {
 
-// In-place exclusive scan of a[0..n) by ONE block (n <= about a million ints: a few passes of 1024 threads).
-__global__ void k_scan_one_block(int *a, int n)
+// In-place exclusive scan of a[0..n) by ONE block of exactly 1024 threads (all 32 warp_sum slots are written every
+// pass); n <= about a million ints: a few passes.
+constexpr int SCAN_THREADS = 1024;
+__global__ void __launch_bounds__(SCAN_THREADS) k_scan_one_block(int *a, int n)
 {
     __shared__ int warp_sum[32];
     __shared__ int carry;
@@ -349,6 +354,15 @@ __global__ void k_task_fill_bounded(int tilem, const int *__restrict__ tile_ptr,
 
 int *g_noalloc_ptr[64];       // device address of g_noalloc_scratch per device, resolved on first use
 bool g_noalloc_ready[64];
+std::mutex g_noalloc_mutex;   // two host threads may make their first call on a device at the same time
+
+// restores the caller's current device when the entry point returns
+struct DeviceGuard
+{
+    int previous = -1;
+    DeviceGuard() { if (cudaGetDevice(&previous) != cudaSuccess) previous = -1; }
+    ~DeviceGuard() { if (previous >= 0) cudaSetDevice(previous); }
+};
 
 }  // namespace
 
@@ -364,8 +378,10 @@ bool g_noalloc_ready[64];
 //   * tilem <= TSP_NOALLOC_MAX_PANELS (1,048,576 panels); more is refused with TSP_EINVAL.  If the schedule
 //     needs more than `capacity` tasks the call returns TSP_ENOMEM, *ntasks holds the number needed and the
 //     output arrays are left untouched.
-//   * The first call on a device looks up the device address of the scratch array (with that device current);
-//     make that first call before starting a stream capture.
+//   * The first call on a device looks up the device address of the scratch array (with that device current) and, with
+//     lazy module loading, is also the call that loads these kernels onto the device -- both may allocate inside the
+//     CUDA runtime.  Make that first call at start-up: before any stream capture, and before the host carves its arena.
+//     Later calls allocate nothing (the GPU test checks that the free device memory does not move).
 //   * All calls share the one scratch array per device.  Each call clears what it needs at its start, so calls
 //     one after another on the same stream are fine; two calls whose kernels can overlap on the GPU (different
 //     streams or threads, same device) race on it and must be serialised by the caller.
@@ -384,14 +400,18 @@ extern "C" int tsp_schedule_noalloc(int device, int tilem, int TH, const int *d_
         tsp_set_error("schedule_noalloc: %d panels exceed the fixed scratch of %d panels; use tsp_schedule()", tilem, TSP_NOALLOC_MAX_PANELS);
         return TSP_EINVAL;
     }
+    DeviceGuard restore_device;
     TSP_CUDA(cudaSetDevice(device));
-    if (!g_noalloc_ready[device])
     {
-        // In host code the array's name is only a handle for the runtime, not a device address.
-        void *p = nullptr;
-        TSP_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-        g_noalloc_ptr[device] = (int *)p;
-        g_noalloc_ready[device] = true;
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ready[device])
+        {
+            // In host code the array's name is only a handle for the runtime, not a device address.
+            void *p = nullptr;
+            TSP_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            g_noalloc_ptr[device] = (int *)p;
+            g_noalloc_ready[device] = true;
+        }
     }
     int *counts = g_noalloc_ptr[device];
     int *split_count = counts + TSP_NOALLOC_MAX_PANELS + 1;
@@ -402,7 +422,7 @@ extern "C" int tsp_schedule_noalloc(int device, int tilem, int TH, const int *d_
     const int T = 256;
     TSP_CUDA(cudaMemsetAsync(split_count, 0, sizeof(int), s));  // the array keeps the previous call's contents
     k_task_counts<<<(tilem + 1 + T - 1) / T, T, 0, s>>>(tilem, d_tile_ptr, TH, counts);
-    k_scan_one_block<<<1, 1024, 0, s>>>(counts, tilem + 1);
+    k_scan_one_block<<<1, SCAN_THREADS, 0, s>>>(counts, tilem + 1);
     k_task_fill_bounded<<<(tilem + T - 1) / T, T, 0, s>>>(tilem, d_tile_ptr, d_panel_row, TH, counts, capacity, d_task_row, d_task_start,
                                                          d_split_row, split_count);
     TSP_CUDA(cudaGetLastError());

@@ -4,22 +4,25 @@
 // Replaces upstream stir_spmm_cuda_kernel_v64* (src/tilespmm_cuda.h:1025-1632) and switch_tilespmm_cuda_v64
 // (src/tilespmm_cuda.h:1710-1744).  Upstream keeps every 64-row tile as a dense, zero-padded 4 KB block
 // (src/csr2tile.h:309-373); on a stencil 95% of those bytes are zeros.  Here a tile is a RECORD in one byte array:
-//   packed record   64 row masks (bit k of mask r: position (r, k) holds an entry; 16-bit masks for TF32 tiles of
-//                   16 columns, 32-bit masks for FP16 tiles of 32 columns) followed by the values of the set
-//                   positions in row-major order, padded to 16 bytes -- for tiles with at most REC_MAX_VALS values;
+//   packed record   for a tile with n <= REC_MAX_VALS entries: n_pad = n rounded up to 8 positions of 16 bits (the
+//                   element index of the entry inside the 4 KB operand tile; 0xffff in the padding) followed by n_pad
+//                   values, both in row-major order of the entries;
 //   dense record    the 4 KB tile in the K-major core-matrix order tcgen05.mma reads -- for fuller tiles.
 // rec[t] is the record's offset in 16-byte units, bit 31 set for a dense record.
 //
 // One CTA owns one task (a 64-row panel or a slice of a split panel) and one column stripe of up to 256 columns, so
 // the tile records and column indices are read once per 256 columns (upstream: once per 64).  Roles:
-//   warps 0-3  producers.  Warp w owns tiles w, w+4, ... of the task.  For its tile it (1) gathers the B rows named by
-//              tile_colidx into the ring slot in the swizzled MN-major operand layout -- 16-byte cp.async, one gathered
-//              row segment per warp instruction, or, in the TMA form, cp.async.bulk.tensor ... tile::gather4 requests
-//              issued by one lane; (2) prefetches the record of its NEXT tile into a private buffer; (3) expands the
-//              record of the current tile into the slot's 4 KB A area in operand order (zero fill + one store per
-//              value), or starts one 4 KB bulk copy for a dense record; (4) publishes the slot on its mbarrier.
-//              Afterwards the four warps are the epilogue: tcgen05.ld of the 64 x N FP32 accumulator -> C.
-//   warp 4     allocates tensor memory; one lane issues two tcgen05.mma (M=64, N=stripe, K=16 FP16 / K=8 TF32) per
+//   warps 0..PW-1   B producers (PW = 8 for stripes of 128 columns and more, else 4).  Together they gather the B rows
+//              named by tile_colidx with 16-byte cp.async straight into the swizzled MN-major operand layout of the ring
+//              slot, every thread a fixed few chunks of every tile, and publish a tile LAG tiles after issuing it.  In the
+//              TMA form one lane issues cp.async.bulk.tensor ... tile::gather4 requests instead.  What bounds a
+//              gather-fed kernel on this GPU is the number of independent warps that issue loads (a warp issues an
+//              instruction every ~11 cycles), which is why the rows of ONE tile are spread over all producer threads.
+//              Warps 0-3 are also the epilogue: tcgen05.ld of the 64 x N FP32 accumulator -> C.
+//   next NE warps  expanders.  Expander e owns tiles e, e+NE, ...: it copies the tile's record into a private buffer one
+//              tile ahead (cp.async) and expands it into the slot's 4 KB A area in operand order -- zero fill plus one
+//              store per value; for a dense record one 4 KB bulk copy -- then arrives on the slot's barrier.
+//   last warp  allocates tensor memory; one lane issues two tcgen05.mma (M=64, N=stripe, K=16 FP16 / K=8 TF32) per
 //              tile and releases ring slots with tcgen05.commit.
 // The accumulator of a whole task stays in tensor memory (64 lanes x N columns) and is written once, with vector
 // stores, or vector red.global.add for the slices of a split panel.
@@ -33,11 +36,8 @@ namespace
 {
 
 constexpr unsigned WAIT_LIMIT = 1u << 22;
-constexpr int PW = 4;                  // producer (and epilogue) warps
-constexpr int THREADS = (PW + 1) * 32;
-
-#ifndef TSP64_DEPTH
-#define TSP64_DEPTH 2                  // tiles a producer warp keeps in flight (1 or 2)
+#ifndef TSP64_NE
+#define TSP64_NE 2                     // expander warps
 #endif
 
 template <int PREC, int N>
@@ -49,21 +49,31 @@ struct Cfg64
     static constexpr int RB = N * SZ;                         // bytes of one gathered row segment
     static constexpr int CPR = RB / 16;                       // 16-byte chunks per row segment
     static constexpr int B_BYTES = BNK * RB;
+    static constexpr int PW = N >= 128 ? 8 : 4;               // B producer warps
+    static constexpr int NE = TSP64_NE;                       // expander warps
+    static constexpr int THREADS = (PW + NE + 1) * 32;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int ITERS = BNK * CPR / 32;              // warp-wide copies per tile
-    static constexpr int DEPTH = TSP64_DEPTH;
+    static constexpr int B_ITERS = (BNK * CPR) / (PW * 32);   // copies per producer thread per tile
+    static constexpr int KPI = PW * 32 / CPR;                 // tile rows covered by one CTA-wide copy
+    // ring depth and how many tiles the producers run ahead of what they have published: a slot is reused
+    // STAGES tiles later, LAG+1 tiles are in flight to memory, and the MMA has STAGES-LAG tiles of slack
 #ifdef TSP64_STAGES
     static constexpr int STAGES = TSP64_STAGES;
 #else
-    static constexpr int STAGES = N == 256 ? 5 : (N == 128 ? (DEPTH == 2 ? 8 : 5) : 8);
+    static constexpr int STAGES = N >= 128 ? 4 : (N == 64 ? 6 : 8);
 #endif
-    static_assert(STAGES > PW, "a producer warp may wait for the slot of its next tile while its previous tile is unpublished");
+#ifdef TSP64_LAG
+    static constexpr int LAG = TSP64_LAG;
+#else
+    static constexpr int LAG = N >= 128 ? 2 : 4;
+#endif
+    static_assert(B_ITERS >= 1 && LAG < STAGES, "unsupported pipeline shape");
     // packed records
     static constexpr int MASK_BYTES = 64 * BNK / 8;           // 128 (TF32) / 256 (FP16)
     static constexpr int REC_MAX_VALS = TSP_REC_MAX_VALS(PREC);
-    static constexpr int REC_BYTES = MASK_BYTES + REC_MAX_VALS * SZ;
+    static constexpr int REC_BYTES = REC_MAX_VALS * (2 + SZ);   // positions + values of the fullest packed record
     static constexpr int REC_CHUNKS = REC_BYTES / 16;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + PW * 2 * REC_BYTES + 1024;  // + slack to align the ring to 1 KB
+    static constexpr int SMEM = STAGES * STAGE_BYTES + NE * 2 * REC_BYTES + 1024;  // + slack to align the ring to 1 KB
     // Shared-memory layout of the gathered rows (the MN-major B operand):
     //   FP16, rows >= 128 B : 128-byte swizzle, atoms of 8 K-rows x 128 B, 16-byte chunks XORed with the row
     //   FP16, 64-byte rows  : 64-byte swizzle, atoms of 8 K-rows x 64 B
@@ -166,6 +176,15 @@ __device__ __forceinline__ void umma_commit(unsigned bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32])
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -188,69 +207,48 @@ __device__ __forceinline__ unsigned b_chunk_offset(int k, int c)
     return ((c >> 3) * C::KATOMS + ka) * 512 + kr * 128 + (((((c & 7) >> 1) ^ kr) << 5) | ((c & 1) << 4));
 }
 
-// Expands the packed record at shared address `rec` into the 4 KB A area at shared address `a` (K-major core
-// matrices, tsp_umma_index): zero fill, then one store per value.  Lane l owns rows 2l and 2l+1, whose values are
-// contiguous in the record, so the position of a lane's first value is the prefix sum of the lanes' entry counts.
+// Expands the packed record at shared address `rec` (n_pad 16-bit positions, then n_pad values) into the 4 KB A area at
+// shared address `a` (K-major core matrices, tsp_umma_index): zero fill, then one store per value.  A position is the
+// element index inside the operand tile, so a lane's work per value is two loads and one store; 0xffff marks padding.
 template <int PREC>
-__device__ __forceinline__ void expand_record(unsigned rec, unsigned a, int lane)
+__device__ __forceinline__ void expand_record(unsigned rec, unsigned n_pad, unsigned a, int lane)
 {
+    constexpr int SZ = PREC == 0 ? 2 : 4;
     __syncwarp();   // the record was copied in by all lanes of the warp
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int q = 0; q < 8; q++)
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(a + (unsigned)(q * 32 + lane) * 16), "r"(zero.x), "r"(zero.y), "r"(zero.z), "r"(zero.w) : "memory");
-    unsigned w0, w1;
-    if constexpr (PREC == 1)
-    {
-        unsigned w;
-        asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(w) : "r"(rec + (unsigned)lane * 4));
-        w0 = w & 0xffffu; w1 = w >> 16;
-    }
-    else
-        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];\n" : "=r"(w0), "=r"(w1) : "r"(rec + (unsigned)lane * 8));
-    const int cnt = __popc(w0) + __popc(w1);
-    int incl = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(a + (unsigned)(q * 32 + lane) * 16), "r"(0u) : "memory");
     __syncwarp();   // the zero fill of every lane is ordered before any lane's value stores
-    constexpr int SZ = PREC == 0 ? 2 : 4, T = 16 / SZ, MASKS = PREC == 0 ? 256 : 128;
-    unsigned src = rec + MASKS + (unsigned)(incl - cnt) * SZ;
-#pragma unroll
-    for (int half = 0; half < 2; half++)
+    const unsigned vals = rec + n_pad * 2;
+    for (unsigned j = lane; j < n_pad; j += 32)
     {
-        unsigned w = half ? w1 : w0;
-        const int r = 2 * lane + half;
-        const unsigned row_off = a + (unsigned)(r >> 3) * 128 + (unsigned)(r & 7) * 16;
-        while (w)
+        unsigned short u;
+        asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(u) : "r"(rec + j * 2));
+        if (u == 0xffffu) continue;
+        if constexpr (PREC == 1)
         {
-            const int k = __ffs(w) - 1;
-            w &= w - 1;
-            const unsigned dst = row_off + (unsigned)(k / T) * 1024 + (unsigned)(k % T) * SZ;
-            if constexpr (PREC == 1)
-            {
-                unsigned v;
-                asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(src));
-                asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(dst), "r"(v) : "memory");
-            }
-            else
-            {
-                unsigned short v;
-                asm volatile("ld.shared.b16 %0, [%1];\n" : "=h"(v) : "r"(src));
-                asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(dst), "h"(v) : "memory");
-            }
-            src += SZ;
+            unsigned v;
+            asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(vals + j * 4));
+            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(a + (unsigned)u * 4), "r"(v) : "memory");
+        }
+        else
+        {
+            unsigned short v;
+            asm volatile("ld.shared.b16 %0, [%1];\n" : "=h"(v) : "r"(vals + j * 2));
+            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(a + (unsigned)u * 2), "h"(v) : "memory");
         }
     }
 }
 
 template <int PREC, int N, bool TMA>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(Cfg64<PREC, N>::THREADS, (Cfg64<PREC, N>::MAX_CTAS_BY_SMEM > 4 ? 4 : Cfg64<PREC, N>::MAX_CTAS_BY_SMEM))
 k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_begin, const unsigned int *__restrict__ task_row,
          const int *__restrict__ task_start, const int *__restrict__ tile_colidx, const unsigned int *__restrict__ rec_ptr,
-         const unsigned char *__restrict__ pack, const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err)
+         const unsigned char *__restrict__ pack, const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err,
+         const TspBounds bounds)
 {
     using C = Cfg64<PREC, N>;
-    constexpr int S = C::STAGES, D = C::DEPTH;
+    constexpr int S = C::STAGES, PW = C::PW, NE = C::NE;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * C::STAGES + 1];
     __shared__ unsigned tmem_slot;
@@ -258,21 +256,33 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int task = blockIdx.x, stripe = blockIdx.y;
     const unsigned ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const unsigned recs = ring + S * C::STAGE_BYTES;      // 2 record buffers per producer warp
+    const unsigned recs = ring + S * C::STAGE_BYTES;      // two record buffers per expander warp
     const unsigned bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]), bar_done = smem_u32(&bars[2 * S]);
 
     const unsigned int trow = task_row[task];
     const bool split = (trow >> 31) != 0;
     const int first_row = (int)(trow & 0x7fffffffu) - row_begin;
-    const int t0 = task_start[task], nt = task_start[task + 1] - t0;
+    int t0 = task_start[task], nt = task_start[task + 1] - t0;
+    if (TSP_CHECKED)
+    {
+        // checked build: the task must lie inside the class's tiles and its 64 rows inside the caller's C
+        const bool bad_task = t0 < 0 || nt < 0 || (long long)t0 + nt > bounds.tilenum, bad_rows = first_row < 0 || first_row + 64 > bounds.c_rows;
+        if (bad_task || bad_rows)
+        {
+            if (tid == 0) atomicExch(err, bad_task ? 0x21 : 0x22);
+            return;   // before any barrier or tensor-memory allocation
+        }
+    }
 
+    // a slot is full when the B producers (PW warps, or the one TMA lane) and the tile's expander have arrived
+    constexpr unsigned FULL_COUNT = (TMA ? 1 : PW) + 1;
     if (tid == 0)
     {
-        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, FULL_COUNT); mbar_init(bar_empty + 8 * s, 1); }
         mbar_init(bar_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == PW)
+    if (warp == PW + NE)
     {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_slot)), "r"(C::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -285,140 +295,185 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
 
     if (warp < PW)
     {
-        // ------------------------------------------------------------ producers: warp w owns tiles w, w+PW, ...
-        const unsigned ldb_b = (unsigned)ldb * C::SZ;
-        const unsigned my_recs = recs + (unsigned)warp * 2 * C::REC_BYTES;
-        const int ntw = nt > warp ? (nt - warp + PW - 1) / PW : 0;     // tiles of this warp
-        // lane constants of the gather: copy q = it*32 + lane of a tile is chunk c = q % CPR of row k = q / CPR
-        const int c_lane = C::CPR >= 32 ? lane : lane % C::CPR, k_lane = C::CPR >= 32 ? 0 : lane / C::CPR;
-        const unsigned char *gsrc = dB + (size_t)stripe * C::RB + (size_t)c_lane * 16;
+        // ------------------------------------------------------------ B producers
+        if constexpr (TMA)
+        {
+            // one lane drives the copy engine: per tile one gather4 request per four gathered rows and 128-byte column
+            // block; the bytes are counted on the slot's barrier
+            if (warp == 0)
+            {
+                const int x0 = stripe * N;
+                int idx_next = (nt > 0 && lane < C::BNK) ? __ldg(tile_colidx + (size_t)t0 * C::BNK + lane) : 0;
+                for (int i = 0; i < nt && ok; i++)
+                {
+                    const int s = i % S;
+                    if (i >= S) { ok = mbar_wait_warp(bar_empty + 8 * s, ((i / S) - 1) & 1, lane); if (!ok) break; }
+                    const unsigned st = ring + s * C::STAGE_BYTES + C::A_BYTES, bar = bar_full + 8 * s;
+                    int idx_cur = idx_next;
+                    if (TSP_CHECKED && lane < C::BNK && (unsigned)idx_cur >= (unsigned)bounds.colA) { atomicExch(err, 0x20); idx_cur = 0; }
+                    if (i + 1 < nt && lane < C::BNK) idx_next = __ldg(tile_colidx + (size_t)(t0 + i + 1) * C::BNK + lane);
+                    if (lane == 0) mbar_expect_tx_only(bar, C::B_BYTES);
+                    __syncwarp();
+#pragma unroll
+                    for (int g = 0; g < C::BNK / 4; g++)
+                    {
+                        const int r0 = __shfl_sync(0xffffffffu, idx_cur, 4 * g), r1 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 1);
+                        const int r2 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 3);
+                        // rows 4g .. 4g+3 of the tile; for FP16 two groups share one 8-row atom
+                        const unsigned atom = (unsigned)((g * 4) / C::ATOM_ROWS) * C::ATOM_BYTES + (unsigned)((g * 4) % C::ATOM_ROWS) * C::BOX_BYTES;
+                        if (lane == 0)
+                        {
+#pragma unroll
+                            for (int b = 0; b < C::NBOX; b++)
+                                tma_gather4(st + (unsigned)b * C::KATOMS * C::ATOM_BYTES + atom, &bmap, x0 + b * C::BOX_COLS, r0, r1, r2, r3, bar);
+                        }
+                    }
+                    if (lane == 0) mbar_arrive(bar);
+                }
+            }
+        }
+        else
+        {
+            // Chunk q = it*PW*32 + tid of a tile is 16-byte chunk c = tid % CPR of row k = it*KPI + tid/CPR, so the
+            // source column offset and the swizzled destination of every copy are loop invariants.
+            const unsigned ldb_b = (unsigned)ldb * C::SZ;
+            const int c_mine = tid % C::CPR, k_mine = tid / C::CPR;
+            const unsigned char *gsrc = dB + (size_t)stripe * C::RB + (size_t)c_mine * 16;
+            const int *idx_ptr = tile_colidx + (size_t)t0 * C::BNK + k_mine;
+            int cols_next[C::B_ITERS];
+            unsigned dst_off[C::B_ITERS];
+#pragma unroll
+            for (int it = 0; it < C::B_ITERS; it++)
+            {
+                dst_off[it] = C::A_BYTES + b_chunk_offset<C>(it * C::KPI + k_mine, c_mine);
+                cols_next[it] = nt > 0 ? __ldg(idx_ptr + it * C::KPI) : 0;
+                if (TSP_CHECKED && (unsigned)cols_next[it] >= (unsigned)bounds.colA) { atomicExch(err, 0x20); cols_next[it] = 0; }
+            }
+            auto publish = [&](int i) {  // the B rows of tile i are complete in shared memory
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * (i % S));
+            };
+            int published = 0;
+            for (int i = 0; i < nt && ok; i++)
+            {
+                const int s = i % S;
+                if (i >= S) { ok = mbar_wait_warp(bar_empty + 8 * s, ((i / S) - 1) & 1, lane); if (!ok) break; }
+                const unsigned st = ring + s * C::STAGE_BYTES;
+#pragma unroll
+                for (int it = 0; it < C::B_ITERS; it++)
+                    cp_async16(st + dst_off[it], gsrc + (unsigned long long)(unsigned)cols_next[it] * ldb_b);
+                cp_async_commit();
+                idx_ptr += C::BNK;
+                if (i + 1 < nt)
+                {
+#pragma unroll
+                    for (int it = 0; it < C::B_ITERS; it++)
+                    {
+                        cols_next[it] = __ldg(idx_ptr + it * C::KPI);
+                        if (TSP_CHECKED && (unsigned)cols_next[it] >= (unsigned)bounds.colA) { atomicExch(err, 0x20); cols_next[it] = 0; }
+                    }
+                }
+                if (i >= C::LAG)
+                {
+                    cp_async_wait<C::LAG>();  // the group of tile i-LAG has landed
+                    publish(i - C::LAG);
+                    published = i - C::LAG + 1;
+                }
+            }
+            cp_async_wait<0>();
+            if (ok)
+                for (int i = published; i < nt; i++) publish(i);
+        }
 
-        // state of the tile that will be issued next: its column indices (lane k: row k) and record word
-        int idx_next = 0;
-        unsigned rec_next = 0, rec_next_end = 0;
-        auto fetch_meta = [&](int i) {   // i: tile index within the task
-            const size_t t = (size_t)t0 + i;
-            if (lane < C::BNK) idx_next = __ldg(tile_colidx + t * C::BNK + lane);
-            const unsigned rw = __ldg(rec_ptr + t + (lane & 1));
-            rec_next = __shfl_sync(0xffffffffu, rw, 0);
-            rec_next_end = __shfl_sync(0xffffffffu, rw, 1) & 0x7fffffffu;
+        // ------------------------------------------------------------ epilogue (warps 0-3: tensor-memory quarter = warp)
+        if (warp < 4)
+        {
+            if (ok && nt > 0)
+            {
+                ok = mbar_wait_warp(bar_done, 0, lane);
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            }
+            if (ok)
+            {
+                // with M = 64 the accumulator row r lives in tensor-memory lane (r/16)*32 + r%16
+                const int quarter = warp & 3;
+                const int row = quarter * 16 + (lane & 15);
+                float *crow = dC + (size_t)(first_row + row) * (size_t)ldb + (size_t)stripe * N;
+#pragma unroll 1
+                for (int c0 = 0; c0 < N; c0 += 16)   // 16 columns at a time keeps the kernel within 40 registers (4 CTAs of 11 warps per SM)
+                {
+                    unsigned r[16];
+                    if (nt > 0) tmem_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                    else
+                    {
+#pragma unroll
+                        for (int q = 0; q < 16; q++) r[q] = 0u;
+                    }
+                    if (lane < 16)
+                    {
+#pragma unroll
+                        for (int q = 0; q < 16; q += 4)
+                        {
+                            if (split)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"l"(crow + c0 + q), "f"(__uint_as_float(r[q])),
+                                             "f"(__uint_as_float(r[q + 1])), "f"(__uint_as_float(r[q + 2])), "f"(__uint_as_float(r[q + 3])) : "memory");
+                            else
+                                *reinterpret_cast<uint4 *>(crow + c0 + q) = make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    else if (warp < PW + NE)
+    {
+        // ------------------------------------------------------------ expanders: warp e owns tiles e, e+NE, ...
+        const int e = warp - PW;
+        const unsigned my_recs = recs + (unsigned)e * 2 * C::REC_BYTES;
+        const int nte = nt > e ? (nt - e + NE - 1) / NE : 0;       // tiles of this expander
+        // record words run two tiles ahead in registers, the record itself one tile ahead in shared memory
+        unsigned w_cur = 0, w_cur_end = 0, w_next = 0, w_next_end = 0;
+        auto load_words = [&](int i, unsigned &w, unsigned &w_end) {
+            const unsigned rw = __ldg(rec_ptr + (size_t)t0 + i + (lane & 1));
+            w = __shfl_sync(0xffffffffu, rw, 0);
+            w_end = __shfl_sync(0xffffffffu, rw, 1) & 0x7fffffffu;
         };
-        auto fetch_record = [&](int slot) {   // packed record of the "next" tile -> private buffer `slot` (cp.async, caller commits)
-            if (rec_next >> 31) return;       // dense records go straight into the ring slot
-            const unsigned chunks = min(rec_next_end - (rec_next & 0x7fffffffu), (unsigned)C::REC_CHUNKS);
-            const unsigned char *src = pack + (size_t)(rec_next & 0x7fffffffu) * 16;
+        auto fetch_record = [&](unsigned w, unsigned w_end, int slot) {   // packed record -> private buffer (cp.async, caller commits)
+            if (w >> 31) return;                                         // dense records go straight into the ring slot
+            const unsigned chunks = min(w_end - w, (unsigned)C::REC_CHUNKS);
+            const unsigned char *src = pack + (size_t)w * 16;
             for (unsigned q = lane; q < chunks; q += 32) cp_async16(my_recs + (unsigned)slot * C::REC_BYTES + q * 16, src + (size_t)q * 16);
         };
-        if (ntw > 0)
-        {
-            fetch_meta(warp);
-            fetch_record(0);
-        }
+        if (nte > 0) { load_words(e, w_cur, w_cur_end); fetch_record(w_cur, w_cur_end, 0); }
         cp_async_commit();
-        if (D == 1) cp_async_wait<0>();
-
-        auto publish = [&](int i) {  // tile i is complete in shared memory: hand it to the MMA warp
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full + 8 * (i % S));
-        };
-
-        for (int j = 0; j < ntw; j++)
+        if (nte > 1) load_words(e + NE, w_next, w_next_end);
+        for (int m = 0; m < nte; m++)
         {
-            const int i = warp + j * PW, s = i % S;
+            const int i = e + m * NE, s = i % S;
+            // start the copy of the next record, then make sure this tile's record has landed
+            unsigned w_next2 = 0, w_next2_end = 0;
+            if (m + 1 < nte) fetch_record(w_next, w_next_end, (m + 1) & 1);
+            cp_async_commit();
+            if (m + 2 < nte) load_words(i + 2 * NE, w_next2, w_next2_end);
+            cp_async_wait<1>();
             if (i >= S) { ok = mbar_wait_warp(bar_empty + 8 * s, ((i / S) - 1) & 1, lane); if (!ok) break; }
             const unsigned st = ring + s * C::STAGE_BYTES, bar = bar_full + 8 * s;
-            const int idx_cur = idx_next;
-            const unsigned rec_cur = rec_next;
-            const bool dense = (rec_cur >> 31) != 0;
-            // ---- B rows of tile i
-            if constexpr (TMA)
+            if (w_cur >> 31)
             {
-                if (lane == 0) mbar_expect_tx_only(bar, C::B_BYTES + (dense ? C::A_BYTES : 0));
-                __syncwarp();
-                const int x0 = stripe * N;
-#pragma unroll
-                for (int g = 0; g < C::BNK / 4; g++)
+                if (lane == 0)   // a dense record goes from global memory straight into the A area; its bytes count on the slot's barrier
                 {
-                    const int r0 = __shfl_sync(0xffffffffu, idx_cur, 4 * g), r1 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 1);
-                    const int r2 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, idx_cur, 4 * g + 3);
-                    // rows 4g .. 4g+3 of the tile; for FP16 two groups share one 8-row atom
-                    const unsigned atom = (unsigned)((g * 4) / C::ATOM_ROWS) * C::ATOM_BYTES + (unsigned)((g * 4) % C::ATOM_ROWS) * C::BOX_BYTES;
-                    if (lane == 0)
-                    {
-#pragma unroll
-                        for (int b = 0; b < C::NBOX; b++)
-                            tma_gather4(st + C::A_BYTES + (unsigned)b * C::KATOMS * C::ATOM_BYTES + atom, &bmap, x0 + b * C::BOX_COLS, r0, r1, r2, r3, bar);
-                    }
+                    mbar_expect_tx_only(bar, C::A_BYTES);
+                    bulk_g2s(st, pack + (size_t)(w_cur & 0x7fffffffu) * 16, C::A_BYTES, bar);
                 }
             }
-            else
-            {
-                if (dense && lane == 0) mbar_expect_tx_only(bar, C::A_BYTES);
-#pragma unroll
-                for (int it = 0; it < C::ITERS; it++)
-                {
-                    const int k = C::CPR >= 32 ? it / (C::CPR / 32) : it * (32 / C::CPR) + k_lane;
-                    const int c = C::CPR >= 32 ? (it % (C::CPR / 32)) * 32 + c_lane : c_lane;
-                    const int col = __shfl_sync(0xffffffffu, idx_cur, k);
-                    const size_t extra = C::CPR > 32 ? (size_t)(it % (C::CPR / 32)) * 512 : 0;
-                    cp_async16(st + C::A_BYTES + b_chunk_offset<C>(k, c), gsrc + extra + (unsigned long long)(unsigned)col * ldb_b);
-                }
-            }
-            if (dense && lane == 0) bulk_g2s(st, pack + (size_t)(rec_cur & 0x7fffffffu) * 16, C::A_BYTES, bar);
-            // ---- record and indices of this warp's next tile
-            if (j + 1 < ntw)
-            {
-                fetch_meta(i + PW);
-                fetch_record((j + 1) & 1);
-            }
-            cp_async_commit();
-            if (D == 2) cp_async_wait<1>();     // everything up to the previous iteration's group has landed
-            // ---- A of tile i
-            if (!dense) expand_record<PREC>(my_recs + (unsigned)(j & 1) * C::REC_BYTES, st, lane);
-            if (D == 1) { cp_async_wait<0>(); publish(i); }
-            else if (j > 0) publish(i - PW);
+            else expand_record<PREC>(my_recs + (unsigned)(m & 1) * C::REC_BYTES, min((w_cur_end - w_cur) * 16u / (2 + C::SZ), (unsigned)C::REC_MAX_VALS), st, lane);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar);
+            w_cur = w_next; w_cur_end = w_next_end; w_next = w_next2; w_next_end = w_next2_end;
         }
         cp_async_wait<0>();
-        if (D == 2 && ok && ntw > 0) publish(warp + (ntw - 1) * PW);
-
-        // ------------------------------------------------------------ epilogue
-        if (ok && nt > 0)
-        {
-            ok = mbar_wait_warp(bar_done, 0, lane);
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        }
-        if (ok)
-        {
-            // with M = 64 the accumulator row r lives in tensor-memory lane (r/16)*32 + r%16; a warp reads the 32 lanes
-            // of its quarter (warp % 4)
-            const int quarter = warp & 3;
-            const int row = quarter * 16 + (lane & 15);
-            float *crow = dC + (size_t)(first_row + row) * (size_t)ldb + (size_t)stripe * N;
-#pragma unroll 1
-            for (int c0 = 0; c0 < N; c0 += 32)
-            {
-                unsigned r[32];
-                if (nt > 0) tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
-                else
-                {
-#pragma unroll
-                    for (int q = 0; q < 32; q++) r[q] = 0u;
-                }
-                if (lane < 16)
-                {
-#pragma unroll
-                    for (int q = 0; q < 32; q += 4)
-                    {
-                        if (split)
-                            asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"l"(crow + c0 + q), "f"(__uint_as_float(r[q])),
-                                         "f"(__uint_as_float(r[q + 1])), "f"(__uint_as_float(r[q + 2])), "f"(__uint_as_float(r[q + 3])) : "memory");
-                        else
-                            *reinterpret_cast<uint4 *>(crow + c0 + q) = make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]);
-                    }
-                }
-            }
-        }
     }
     else if (lane == 0)
     {
@@ -451,7 +506,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
     if (!ok) atomicExch(err, 1);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == PW)
+    if (warp == PW + NE)
     {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
@@ -503,14 +558,15 @@ int launch64(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_t 
         configured[h->device & 7] = true;
     }
     if (c.ntasks == 0) return TSP_OK;
+    TspRange range("tsp 64-row class kernel");
     if (TMA && (h->bmap_ptr != d_b || h->bmap_cols != colB || h->bmap_box != C::BOX_COLS))   // the map depends on B's address and shape only
     {
         TSP_TRY(make_b_map(reinterpret_cast<CUtensorMap *>(h->bmap), PREC, d_b, h->colA, colB, C::BOX_COLS, C::BOX_BYTES));
         h->bmap_ptr = d_b; h->bmap_cols = colB; h->bmap_box = C::BOX_COLS;
     }
     dim3 grid(c.ntasks, colB / N);
-    kern<<<grid, THREADS, C::SMEM, s>>>(*reinterpret_cast<const CUtensorMap *>(h->bmap), c.ntasks, colB, h->row_begin, c.d_task_row, c.d_task_start,
-                                       c.d_tile_colidx, c.d_rec, c.d_pack, (const unsigned char *)d_b, d_c, h->d_error);
+    kern<<<grid, C::THREADS, C::SMEM, s>>>(*reinterpret_cast<const CUtensorMap *>(h->bmap), c.ntasks, colB, h->row_begin, c.d_task_row, c.d_task_start,
+                                       c.d_tile_colidx, c.d_rec, c.d_pack, (const unsigned char *)d_b, d_c, h->d_error, tsp_bounds(h, 0));
     TSP_CUDA(cudaGetLastError());
     h->launches++;
     return TSP_OK;
@@ -535,7 +591,7 @@ void resources64(TspKernelResources *out)
     cudaFuncAttributes attr;
     memset(&attr, 0, sizeof(attr));
     cudaFuncGetAttributes(&attr, k_spmm64<PREC, N, false>);
-    out->threads = THREADS;
+    out->threads = C::THREADS;
     out->registers_per_thread = attr.numRegs;
     out->shared_bytes = C::SMEM + (long long)attr.sharedSizeBytes;
     out->tasks_per_block = 1;

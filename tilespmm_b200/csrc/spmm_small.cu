@@ -126,7 +126,7 @@ template <int PREC, int CLS, int NS, bool COOP>
 __global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const uint4 *__restrict__ task_pack,
              const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
-             const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err)
+             const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err, const TspBounds bounds)
 {
     using Cfg = SmallCfg<PREC, CLS, NS>;
     constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES, RBS = Cfg::RBS;
@@ -144,7 +144,20 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     // tiles of this warp: t0, t0 + TS, ... (TS = 1: all tiles of the task)
     constexpr int TS = COOP ? WARPS : 1;
     const int t0 = (int)tp.y + (COOP ? warp : 0);
-    const int nt = (int)tp.z > t0 ? ((int)tp.z - t0 + TS - 1) / TS : 0;
+    int nt = (int)tp.z > t0 ? ((int)tp.z - t0 + TS - 1) / TS : 0;
+    bool checked_skip = false;
+    if (TSP_CHECKED)
+    {
+        // checked build: the task must lie inside the class's tiles and its rows inside the caller's C; a task that
+        // does not is reported and multiplies nothing (it still takes part in the block's barriers)
+        const bool bad_task = (int)tp.y < 0 || (int)tp.z < (int)tp.y || (int)tp.z > bounds.tilenum, bad_rows = first_row < 0 || first_row + BM > bounds.c_rows;
+        if (bad_task || bad_rows)
+        {
+            if (lane == 0) atomicExch(err, bad_task ? 0x21 : 0x22);
+            nt = 0;
+            checked_skip = true;   // nothing of this task is stored either
+        }
+    }
     const size_t stripe_bytes = (size_t)stripe * NS * SZ;
     const size_t ldb_bytes = (size_t)ldb * SZ;
 
@@ -167,6 +180,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     const int *idx_ptr = tile_colidx + (size_t)t0 * BN + lane;
     // column index of tile row `lane` for the tile that will be issued next
     int idx_next = (nt > 0 && lane < BN) ? __ldg(idx_ptr) : 0;
+    if (TSP_CHECKED && (unsigned)idx_next >= (unsigned)bounds.colA) { atomicExch(err, 0x20); idx_next = 0; }
 
     const unsigned bars = ring_s + STAGES * Cfg::STAGE_BYTES;
     if (BULK)
@@ -207,6 +221,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         }
         idx_ptr += TS * BN;
         if (i + 1 < nt && lane < BN) idx_next = __ldg(idx_ptr);
+        if (TSP_CHECKED && (unsigned)idx_next >= (unsigned)bounds.colA) { atomicExch(err, 0x20); idx_next = 0; }
     };
     // byte offset of 16-byte chunk `chunk` of gathered row k inside the B part of a slot
     auto boff = [&](int k, int chunk) -> int { return BULK ? k * RBS + chunk * 16 : k * RB + swz<RB>(chunk, k) * 16; };
@@ -332,6 +347,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
                 acc[i][0] += v.x; acc[i][1] += v.y; acc[i][2] += v.z; acc[i][3] += v.w;
             }
     }
+    if (TSP_CHECKED && checked_skip) return;
     // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
     const size_t ldc = (size_t)ldb;
     float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
@@ -431,13 +447,14 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
     const int nstripes = colB / NS;
     const long long units = (long long)c.ntasks * nstripes;
     if (units == 0) return TSP_OK;
+    TspRange range(CLS == 1 ? "tsp 16-row class kernel" : "tsp 8-row class kernel");
     // One warp per unit fills the GPU only when there are several units per resident warp slot; below that (small
     // matrices) a CTA per unit with the tiles dealt out to its four warps is faster.  Tasks of one or two tiles gain nothing.
     const long long warp_slots = (long long)h->prop.multiProcessorCount * (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4) * WARPS;
     const bool coop = units * WARPS <= warp_slots && (long long)c.tilenum >= 3 * (long long)c.ntasks;
     const int grid = coop ? (int)units : (int)((units + WARPS - 1) / WARPS);
     (coop ? kern_coop : kern)<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_pack, c.d_tile_colidx,
-                                            (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error);
+                                            (const unsigned char *)c.d_val, (const unsigned char *)d_b, d_c, h->d_error, tsp_bounds(h, CLS));
     TSP_CUDA(cudaGetLastError());
     h->launches++;
     return TSP_OK;

@@ -163,7 +163,7 @@ extern "C" int tsp_load(tsp_handle *h, const char *path)
                     int n = 0;
                     for (int b = 0; b < mb; b++) n += __builtin_popcount(masks[(size_t)t * mb + b]);
                     good = n <= TSP_REC_MAX_VALS(h->precision);
-                    units = (unsigned long long)(mb + ((n * (int)vsz + 15) & ~15)) / 16;
+                    units = tsp_packed_units(h->precision, n);
                 }
                 good = good && off == at;
                 at += units;

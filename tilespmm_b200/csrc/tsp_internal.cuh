@@ -79,6 +79,12 @@ __host__ __device__ inline int tsp_device_index(int precision, int cls, int r, i
 // as a dense 4 KB tile.
 #define TSP_REC_MAX_VALS(PREC) ((PREC) == 0 ? 256 : 128)
 __host__ __device__ inline int tsp_mask_bytes(int precision) { return precision == 0 ? 256 : 128; }
+// A packed record holds n_pad = n rounded up to 8 entries: n_pad 16-bit positions (the element index of the value in
+// the 4 KB operand tile, tsp_umma_index; 0xffff in the padding) followed by n_pad values.  Size in 16-byte units:
+__host__ __device__ inline unsigned int tsp_packed_units(int precision, int n)
+{
+    return (unsigned int)(((n + 7) & ~7) * (2 + (precision ? 4 : 2))) / 16u;
+}
 
 // Width of the column stripe one task unit covers for (class, padded dense width): the 64-row kernel keeps up to
 // 256 accumulator columns in tensor memory, the 16/8-row kernels up to 128 in registers.
@@ -88,6 +94,31 @@ __host__ __device__ inline int tsp_stripe_width(int cls, int colB)
     if (cls == 0) return colB % 256 == 0 ? 256 : (colB % 128 == 0 ? 128 : 64);
     return colB % 128 == 0 ? 128 : 64;
 }
+
+// ---------------------------------------------------------------- tracing and the checked build
+
+// NVTX ranges (header-only; a no-op unless a profiler is attached) around conversion stages, scheduling and the class
+// kernels, so that a timeline shows the same phases this library reports.
+#include <nvtx3/nvToolsExt.h>
+struct TspRange
+{
+    explicit TspRange(const char *name) { nvtxRangePushA(name); }
+    ~TspRange() { nvtxRangePop(); }
+};
+
+// What a kernel needs to check its own indices in the checked build (-DTSP_DEBUG, libtilespmm_b200_debug.so): every
+// gathered B row must lie inside B, every task inside the class's tiles, every written C row inside the caller's C.
+// A violation is recorded in the handle's error flag (codes 0x20..0x22, reported as TSP_EINVAL by tsp_check_error) and
+// the access is skipped or redirected to row 0 -- never performed.  The release build passes the struct and ignores it.
+struct TspBounds
+{
+    int colA, tilenum, c_rows;
+};
+#ifdef TSP_DEBUG
+#define TSP_CHECKED 1
+#else
+#define TSP_CHECKED 0
+#endif
 
 // ---------------------------------------------------------------- handle
 
@@ -178,3 +209,7 @@ bool tsp_small_t_supported(int colB);
 int tsp_launch_clear(tsp_handle *h, float *d_c, int colB, cudaStream_t s);
 int tsp_launch_selftest_wait(tsp_handle *h, unsigned polls, cudaStream_t s);
 void tsp_kernel_resources(int precision, int cls, int colB, TspKernelResources *out);
+inline TspBounds tsp_bounds(const tsp_handle *h, int cls)
+{
+    return TspBounds{h->colA, h->cls[cls].tilenum, (int)(((long long)(h->row_end - h->row_begin) + 64) / 64 * 64)};
+}
