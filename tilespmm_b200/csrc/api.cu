@@ -95,7 +95,7 @@ extern "C" int tsp_destroy(tsp_handle *h)
     if (!h) return TSP_OK;
     cudaSetDevice(h->device);
     cudaDeviceSynchronize();
-    tsp_free_tiles(h);
+    tsp_free_tiles(h, true);
     tsp_free_workspace(h);
     if (h->h_pin) cudaFreeHost(h->h_pin);
     for (int i = 0; i < 2; i++) { if (h->side[i]) cudaStreamDestroy(h->side[i]); if (h->join[i]) cudaEventDestroy(h->join[i]); }

@@ -23,6 +23,8 @@
 // Host side: all scratch comes from a workspace kept in the handle (no cudaMalloc/cudaFree per stage), the tile
 // arrays of all classes are one allocation, and the host reads back a handful of scalars in three small copies.
 #include <cub/cub.cuh>
+#include <stdlib.h>
+#include <sys/time.h>
 
 #include "tsp_internal.cuh"
 
@@ -139,38 +141,41 @@ __global__ void k_low_words(const unsigned long long *__restrict__ keys, const i
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = (int)(unsigned int)keys[i];
 }
 
-// ---- stage 2: distinct columns of windows of 2 and 8 consecutive blocks (one warp per window)
+// ---- stage 2: distinct columns of windows of 2 and 8 consecutive blocks
+//
+// A column that occurs in block j counts once in every window [b, b+span) that contains j but not the previous block p
+// that holds the same column: b in (max(p, j-span), j].  So every (block, column) pair adds +1 at max(p, j-span)+1 and -1
+// at j+1 of a difference array, and a prefix sum gives the exact distinct count of every window.  The previous block of
+// every pair comes from one more radix sort, by (column, block).  Work is linear in the number of pairs, whatever the
+// row lengths (a warp per window with searches in the earlier lists took 39 ms on a scale-20 R-MAT graph; this takes 2).
 
-__global__ void k_window_counts(int nb8, int rowA, const int *__restrict__ u8_ptr, const int *__restrict__ ucols,
-                                int *__restrict__ n16, int *__restrict__ n64, int want64)
+__global__ void k_col_block_keys(const unsigned long long *__restrict__ ukeys, int n, int block_bits, unsigned long long *__restrict__ out)
 {
-    const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; b < nb8; b += warps)
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long k = ukeys[i];
+    out[i] = ((k & 0xffffffffull) << block_bits) | (k >> 32);
+}
+
+__global__ void k_window_diffs(const unsigned long long *__restrict__ by_col, int n, int block_bits, int want64, int *__restrict__ d16,
+                               int *__restrict__ d64)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long mask = (1ull << block_bits) - 1ull, k = by_col[i];
+    const int j = (int)(k & mask);
+    int p = -1;
+    if (i > 0)
     {
-        for (int pass = 0; pass < 2; pass++)
-        {
-            const int span = pass == 0 ? 2 : 8;
-            if (pass == 1 && !want64) break;
-            if ((long long)b * 8 + span * 8 > rowA) continue;  // upstream tests need the whole window inside the matrix
-            const int g0 = u8_ptr[b], g1 = u8_ptr[b + span];
-            int dup = 0;
-            for (int g = g0 + lane; g < g1; g += 32)
-            {
-                int j = 1;
-                while (j < span && g >= u8_ptr[b + j]) j++;
-                j -= 1;  // the element belongs to block b + j
-                const int col = ucols[g];
-                for (int q = 0; q < j; q++)  // present in an earlier block of the window?
-                {
-                    const int s = u8_ptr[b + q], len = u8_ptr[b + q + 1] - s;
-                    const int pos = lower_bound_dev(ucols + s, len, col);
-                    if (pos < len && ucols[s + pos] == col) { dup++; break; }
-                }
-            }
-            for (int o = 16; o > 0; o >>= 1) dup += __shfl_xor_sync(0xffffffffu, dup, o);
-            if (lane == 0) (pass == 0 ? n16 : n64)[b] = (g1 - g0) - dup;
-        }
+        const unsigned long long q = by_col[i - 1];
+        if ((q >> block_bits) == (k >> block_bits)) p = (int)(q & mask);
+    }
+    atomicAdd(&d16[max(p, j - 2) + 1], 1);
+    atomicAdd(&d16[j + 1], -1);
+    if (want64)
+    {
+        atomicAdd(&d64[max(p, j - 8) + 1], 1);
+        atomicAdd(&d64[j + 1], -1);
     }
 }
 
@@ -697,15 +702,27 @@ void tsp_free_workspace(tsp_handle *h)
     h->ws_chunks.clear();
 }
 
-void tsp_free_tiles(tsp_handle *h)
+void tsp_free_tiles(tsp_handle *h, bool release)
 {
-    cudaFree(h->tile_block); cudaFree(h->pack_block);
-    h->tile_block = h->pack_block = nullptr;
+    if (release)
+    {
+        cudaFree(h->tile_block); cudaFree(h->pack_block);
+        h->tile_block = h->pack_block = nullptr;
+        h->tile_block_bytes = h->pack_block_bytes = 0;
+    }
     for (int k = 0; k < 3; k++)
     {
         TspClass &c = h->cls[k];
-        cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_split_row); cudaFree(c.d_task_count); cudaFree(c.d_task_pack);
-        c = TspClass();
+        TspClass fresh;
+        if (release) { cudaFree(c.d_task_row); cudaFree(c.d_task_start); cudaFree(c.d_split_row); cudaFree(c.d_task_count); cudaFree(c.d_task_pack); }
+        else
+        {
+            // the schedule arrays and their capacities survive: cudaFree/cudaMalloc per conversion cost more than the conversion kernels
+            fresh.d_task_row = c.d_task_row; fresh.d_task_start = c.d_task_start; fresh.d_split_row = c.d_split_row;
+            fresh.d_task_count = c.d_task_count; fresh.d_task_pack = c.d_task_pack;
+            fresh.cap_tasks = c.cap_tasks; fresh.cap_panels = c.cap_panels;
+        }
+        c = fresh;
         c.BM = tsp_bm(k);
         c.BN = tsp_bn(h->precision, k);
     }
@@ -732,10 +749,14 @@ int tsp_alloc_tile_arrays(tsp_handle *h)
                           : take((size_t)c.tilenum * c.BM * c.BN * vsz + 16);         // dense values
         at[k][5] = k == 0 ? take(((size_t)c.tilenum + 1) * 4) : 0;                    // rec
     }
-    cudaFree(h->tile_block);
-    h->tile_block = nullptr;
-    cudaError_t e = cudaMalloc(&h->tile_block, off);
-    if (e != cudaSuccess) { tsp_set_error("tile arrays: cudaMalloc of %zu bytes failed: %s", off, cudaGetErrorString(e)); return TSP_ENOMEM; }
+    if (off > h->tile_block_bytes || off < h->tile_block_bytes / 4)   // reuse what fits, unless it is far too large
+    {
+        cudaFree(h->tile_block);
+        h->tile_block = nullptr; h->tile_block_bytes = 0;
+        cudaError_t e = cudaMalloc(&h->tile_block, off);
+        if (e != cudaSuccess) { tsp_set_error("tile arrays: cudaMalloc of %zu bytes failed: %s", off, cudaGetErrorString(e)); return TSP_ENOMEM; }
+        h->tile_block_bytes = off;
+    }
     unsigned char *base = static_cast<unsigned char *>(h->tile_block);
     for (int k = 0; k < 3; k++)
     {
@@ -760,10 +781,15 @@ int tsp_alloc_tile_arrays(tsp_handle *h)
 
 int tsp_alloc_pack(tsp_handle *h, long long bytes)
 {
-    cudaFree(h->pack_block);
-    h->pack_block = nullptr;
-    cudaError_t e = cudaMalloc(&h->pack_block, (size_t)bytes + 16);
-    if (e != cudaSuccess) { tsp_set_error("64-row records: cudaMalloc of %lld bytes failed: %s", bytes, cudaGetErrorString(e)); return TSP_ENOMEM; }
+    const size_t want = (size_t)bytes + 16;
+    if (want > h->pack_block_bytes || want < h->pack_block_bytes / 4)
+    {
+        cudaFree(h->pack_block);
+        h->pack_block = nullptr; h->pack_block_bytes = 0;
+        cudaError_t e = cudaMalloc(&h->pack_block, want);
+        if (e != cudaSuccess) { tsp_set_error("64-row records: cudaMalloc of %lld bytes failed: %s", bytes, cudaGetErrorString(e)); return TSP_ENOMEM; }
+        h->pack_block_bytes = want;
+    }
     TSP_CUDA(cudaMemsetAsync(h->pack_block, 0, (size_t)bytes + 16, 0));
     h->cls[0].d_pack = static_cast<unsigned char *>(h->pack_block);
     h->cls[0].pack_bytes = bytes;
@@ -818,6 +844,19 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     int *pin = nullptr;
     TSP_TRY(pinned(h, &pin));
 
+    // TSP_CONVERT_TRACE=1: wall time of every phase on stderr (each mark waits for the stream, so the total grows a little)
+    static const bool trace = getenv("TSP_CONVERT_TRACE") != nullptr;
+    struct timeval tv0;
+    gettimeofday(&tv0, nullptr);
+    auto mark = [&](const char *what) {
+        if (!trace) return;
+        cudaStreamSynchronize(st);
+        struct timeval tv1;
+        gettimeofday(&tv1, nullptr);
+        fprintf(stderr, "  convert %-28s %8.3f ms\n", what, (tv1.tv_sec - tv0.tv_sec) * 1e3 + (tv1.tv_usec - tv0.tv_usec) * 1e-3);
+        tv0 = tv1;
+    };
+
     int fixed = -1;  // src/hetero_split.h:152-169
     if (gamma <= 0.0f) fixed = 0;
     else if (gamma >= 4.0f && delta <= 0.0f) fixed = 1;
@@ -829,13 +868,19 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     const size_t cub_bytes = sort_unique_scratch_bytes(nnz > nb8 + 2 ? nnz : nb8 + 2);
     {
         const size_t n = (size_t)(nnz ? nnz : 1), b = (size_t)nb8 + 16;
-        size_t need = 2 * n * 8 + 2 * n * 4 + b * (4 * 9 + 3) + (size_t)nchunk * (8 + 96 + 4 + 12) + b * 8 + cub_bytes + 64 * 256 + (1 << 16);
+        size_t need = 3 * n * 8 + 2 * n * 4 + b * (4 * 9 + 3) + (size_t)nchunk * (8 + 96 + 4 + 12) + b * 8 + cub_bytes + 64 * 256 + (1 << 16);
         if (csr_on_host) need += ((size_t)rowA + 1) * 4 + n * (4 + (prec ? 4 : 2)) + 1024;
         TSP_TRY(reserve_workspace(h, need));
     }
     Workspace ws(h);
     const int *d_rowptr = rowptr_in, *d_colidx = colidx_in;
     const void *d_val = val_in;
+    bool values_pending = false, values_in_flight = false;
+    struct CopyGuard   // the copy of the values reads caller memory: it must be over on every way out of this function
+    {
+        tsp_handle *h; bool *active;
+        ~CopyGuard() { if (*active) cudaStreamSynchronize(h->side[0]); }
+    } copy_guard{h, &values_pending};
     if (csr_on_host)   // upload of the CSR into the workspace
     {
         int *rp, *ci;
@@ -844,26 +889,40 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         TSP_TRY(ws.get(&rp, (size_t)rowA + 1)); TSP_TRY(ws.get(&ci, nnz)); TSP_TRY(ws.get(&vv, (size_t)nnz * vsz));
         TSP_CUDA(cudaMemcpyAsync(rp, rowptr_in, ((size_t)rowA + 1) * 4, cudaMemcpyHostToDevice, st));
         if (nnz) TSP_CUDA(cudaMemcpyAsync(ci, colidx_in, (size_t)nnz * 4, cudaMemcpyHostToDevice, st));
-        if (nnz) TSP_CUDA(cudaMemcpyAsync(vv, val_in, (size_t)nnz * vsz, cudaMemcpyHostToDevice, st));
         d_rowptr = rp; d_colidx = ci; d_val = vv;
+        values_pending = nnz > 0;   // the values are not needed before stage 5: their upload overlaps the partition kernels
     }
-    unsigned long long *keys, *keys_tmp, *class_rows_nnz;
+    auto upload_values = [&]() -> int {
+        if (!values_pending || values_in_flight) return TSP_OK;
+        TSP_CUDA(cudaMemcpyAsync(const_cast<void *>(d_val), val_in, (size_t)nnz * (prec ? 4 : 2), cudaMemcpyHostToDevice, h->side[0]));
+        TSP_CUDA(cudaEventRecord(h->join[0], h->side[0]));
+        values_in_flight = true;
+        return TSP_OK;
+    };
+    auto wait_values = [&]() -> int {   // orders what is launched on st from here on behind the copy of the values
+        if (values_in_flight) TSP_CUDA(cudaStreamWaitEvent(st, h->join[0], 0));
+        values_in_flight = false;
+        return TSP_OK;
+    };
+    unsigned long long *keys, *keys_tmp, *keys_col = nullptr, *class_rows_nnz;
     int *u8_ptr, *ucols, *n16, *n64, *entry, *base, *counts, *seq_blk, *seq_idx, *blk_seq, *scalars, *pptr_buf, *pcols_buf, *seq_tiles;
     unsigned char *cls_of, *exit_off, *seq_cls, *cub_tmp;
     double *cost;
     TSP_TRY(ws.get(&keys, nnz)); TSP_TRY(ws.get(&keys_tmp, nnz)); TSP_TRY(ws.get(&u8_ptr, (size_t)nb8 + 9)); TSP_TRY(ws.get(&ucols, nnz));
-    TSP_TRY(ws.get(&n16, nb8)); TSP_TRY(ws.get(&n64, nb8)); TSP_TRY(ws.get(&cls_of, nb8));
+    TSP_TRY(ws.get(&n16, (size_t)nb8 + 2)); TSP_TRY(ws.get(&n64, (size_t)nb8 + 2)); TSP_TRY(ws.get(&cls_of, nb8));
     TSP_TRY(ws.get(&exit_off, (size_t)nchunk * 8)); TSP_TRY(ws.get(&counts, (size_t)nchunk * 24)); TSP_TRY(ws.get(&entry, nchunk));
     TSP_TRY(ws.get(&base, (size_t)nchunk * 3 + 3));
     TSP_TRY(ws.get(&seq_blk, nb8)); TSP_TRY(ws.get(&seq_cls, nb8)); TSP_TRY(ws.get(&seq_idx, nb8)); TSP_TRY(ws.get(&blk_seq, nb8));
     TSP_TRY(ws.get(&class_rows_nnz, 6)); TSP_TRY(ws.get(&scalars, 64)); TSP_TRY(ws.get(&cub_tmp, cub_bytes));
     TSP_TRY(ws.get(&pptr_buf, (size_t)nb8 + 1)); TSP_TRY(ws.get(&pcols_buf, nnz)); TSP_TRY(ws.get(&seq_tiles, nb8));
     TSP_TRY(ws.get(&cost, nb8));
+    if (want16 || want64) TSP_TRY(ws.get(&keys_col, nnz));
     // scalars: [0] distinct (8-row block, column) pairs, [1] CSR check, [2] distinct (panel, column) pairs, [8..17] shard cuts
     int *d_nu = scalars, *d_bad = scalars + 1, *d_np = scalars + 2, *d_cuts = scalars + 8;
     TSP_CUDA(cudaMemsetAsync(scalars, 0, 64 * sizeof(int), st));
     TSP_CUDA(cudaMemsetAsync(class_rows_nnz, 0, 6 * sizeof(unsigned long long), st));
 
+    mark("workspace + upload");
     // ---- stage 1: sorted distinct columns of every 8-row block
     nvtxRangePushA("tsp convert: partition (stages 1-3)");
     {
@@ -872,6 +931,12 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         TSP_CUDA(cudaGetLastError());
         if (nnz > 0) TSP_TRY(sort_unique_keys(keys, keys_tmp, nnz, 32 + bits_for((unsigned long long)nb8), cub_tmp, cub_bytes, d_nu));
     }
+    {
+        // the values go up on a side stream while the partition kernels run
+        const int rc_up = upload_values();
+        if (rc_up != TSP_OK) { nvtxRangePop(); return rc_up; }
+    }
+    mark("stage 1 keys+sort+unique");
     k_group_offsets<<<blocks_for(nb8 + 9, T), T, 0, st>>>(keys, d_nu, nb8, 8, u8_ptr);   // windows near the end index past nb8
     if (nnz > 0) k_low_words<<<blocks_for(nnz, T) > 148 * 16 ? 148 * 16 : blocks_for(nnz, T), T, 0, st>>>(keys, d_nu, ucols);
     TSP_CUDA(cudaGetLastError());
@@ -879,11 +944,32 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     // ---- stage 2 + 3: window counts, decisions, chain
     if (want16 || want64)
     {
-        TSP_CUDA(cudaMemsetAsync(n16, 0, (size_t)nb8 * 4, st)); TSP_CUDA(cudaMemsetAsync(n64, 0, (size_t)nb8 * 4, st));
-        const int blocks = blocks_for((long long)nb8 * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)nb8 * 32, T);
-        k_window_counts<<<blocks, T, 0, st>>>(nb8, rowA, u8_ptr, ucols, n16, n64, want64 ? 1 : 0);
-        TSP_CUDA(cudaGetLastError());
+        // read-back 0 (only when windows are compared at all): the number of pairs, and the CSR check
+        TSP_CUDA(cudaMemcpyAsync(pin, scalars, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+        TSP_CUDA(cudaStreamSynchronize(st));
+        if (pin[1])
+        {
+            nvtxRangePop();
+            tsp_set_error("convert: the CSR is inconsistent (row pointers must start at 0, not decrease and end at nnz; columns must lie in [0, %d))", colA);
+            return TSP_EINVAL;
+        }
+        const int pairs = pin[0], bb = bits_for((unsigned long long)nb8);
+        TSP_CUDA(cudaMemsetAsync(n16, 0, ((size_t)nb8 + 2) * 4, st)); TSP_CUDA(cudaMemsetAsync(n64, 0, ((size_t)nb8 + 2) * 4, st));
+        if (pairs > 0)
+        {
+            k_col_block_keys<<<blocks_for(pairs, T), T, 0, st>>>(keys, pairs, bb, keys_tmp);
+            cub::DoubleBuffer<unsigned long long> db(keys_tmp, keys_col);
+            size_t bytes = cub_bytes;
+            TSP_CUDA(cub::DeviceRadixSort::SortKeys(cub_tmp, bytes, db, pairs, 0, bb + bits_for((unsigned long long)colA), st));
+            k_window_diffs<<<blocks_for(pairs, T), T, 0, st>>>(db.Current(), pairs, bb, want64 ? 1 : 0, n16, n64);
+            TSP_CUDA(cudaGetLastError());
+            bytes = cub_bytes;
+            TSP_CUDA(cub::DeviceScan::InclusiveSum(cub_tmp, bytes, n16, n16, nb8 + 1, st));
+            bytes = cub_bytes;
+            if (want64) TSP_CUDA(cub::DeviceScan::InclusiveSum(cub_tmp, bytes, n64, n64, nb8 + 1, st));
+        }
     }
+    mark("stage 2 window counts");
     k_decide<<<blocks_for(nb8, T), T, 0, st>>>(nb8, rowA, gamma, delta, fixed, u8_ptr, n16, n64, cls_of);
     k_chain_local<<<blocks_for((long long)nchunk * 8, T), T, 0, st>>>(nb8, nchunk, cls_of, exit_off, counts);
     k_chain_compose<<<1, 32, 0, st>>>(nchunk, exit_off, counts, entry, base);
@@ -896,6 +982,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     TSP_CUDA(cudaMemcpyAsync(pin + 8, class_rows_nnz, 6 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
     TSP_CUDA(cudaStreamSynchronize(st));
     nvtxRangePop();
+    mark("stage 3 decide+chain+readback");
     const int nu = pin[0];
     if (pin[1])
     {
@@ -929,6 +1016,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     if (nseq) k_seq_tiles<<<blocks_for(nseq, T), T, 0, st>>>(nseq, pptr, seq_cls, prec, seq_tiles);
     TSP_CUDA(cudaGetLastError());
 
+    mark("stage 4 panel lists");
     // ---- shard selection: a contiguous range of the panel sequence, balanced by tile bytes (on the device)
     int s0 = 0, s1 = nseq, p0[3] = {0, 0, 0}, p1[3] = {totals[0], totals[1], totals[2]};
     h->row_begin = 0; h->row_end = rowA;
@@ -998,8 +1086,10 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         c.nnz = (long long)tot_rows_nnz[k * 2 + 1];
     }
 
+    mark("shards + tile_ptr + readback");
     // ---- the tile arrays of all classes: one allocation
     TSP_TRY(tsp_alloc_tile_arrays(h));
+    mark("allocate + clear tile arrays");
     for (int k = 0; k < 3; k++)
     {
         TspClass &c = h->cls[k];
@@ -1014,6 +1104,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
                                             h->cls[2].d_tile_colidx);
         TSP_CUDA(cudaGetLastError());
         // ---- stage 5
+        TSP_TRY(wait_values());
         const int vblocks = blocks_for((long long)rowA * 32, T) > 148 * 64 ? 148 * 64 : blocks_for((long long)rowA * 32, T);
         if (prec == 0)
             k_place_values<__half><<<vblocks, T, 0, st>>>(rowA, 0, s0, s1, d_rowptr, d_colidx, (const __half *)d_val, blk_seq, seq_cls, seq_idx,
@@ -1027,6 +1118,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
                                                          (unsigned int *)h->cls[0].d_bitmap, (float *)h->cls[1].d_val, (float *)h->cls[2].d_val);
         TSP_CUDA(cudaGetLastError());
     }
+    mark("stage 5 colidx + values");
     for (int k = 0; k < 3; k++)  // tile_nnz: exclusive scan over tilenum+1 entries (src/csr2tile.h:786)
     {
         TspClass &c = h->cls[k];
@@ -1078,6 +1170,7 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
         }
     }
     TSP_CUDA(cudaStreamSynchronize(st));
+    mark("stage 6 records");
     // a large workspace (hundreds of millions of entries) is given back; a small one stays for the next conversion
     size_t held = 0;
     for (auto &ch : h->ws_chunks) held += ch.second;

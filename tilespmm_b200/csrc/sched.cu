@@ -124,10 +124,13 @@ int tsp_schedule(tsp_handle *h, int cls, int TH)
     TspClass &c = h->cls[cls];
     c.TH = TH; c.ntasks = 0; c.nsplit = 0;
     if (c.tilem == 0) return TSP_OK;
-    if (!c.d_task_count)
+    if (!c.d_task_count || c.tilem > c.cap_panels)
     {
+        cudaFree(c.d_task_count); cudaFree(c.d_split_row);
+        c.d_task_count = nullptr; c.d_split_row = nullptr; c.cap_panels = 0;
         TSP_CUDA(cudaMalloc((void **)&c.d_task_count, ((size_t)c.tilem + 2) * 4));
         TSP_CUDA(cudaMalloc((void **)&c.d_split_row, ((size_t)c.tilem + 1) * 4));
+        c.cap_panels = c.tilem;
     }
     const int T = 256;
     k_task_counts<<<(c.tilem + 1 + T - 1) / T, T>>>(c.tilem, c.d_tile_ptr, TH, c.d_task_count);

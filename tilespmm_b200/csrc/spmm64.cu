@@ -100,6 +100,25 @@ __device__ __forceinline__ void cp_async16(unsigned smem, const void *gmem)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem), "l"(gmem));
 }
+// The same copy with an L2 eviction policy: gathered rows of B are re-read many times per product and by every later
+// product, a tile record and a row of C pass through once -- with B about the size of the L2, letting the one-pass data
+// go first keeps most of B resident.
+__device__ __forceinline__ void cp_async16_hint(unsigned smem, const void *gmem, unsigned long long policy)
+{
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "l"(policy));
+}
+__device__ __forceinline__ unsigned long long policy_evict_first()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long policy_evict_last()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int K>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(K) : "memory"); }
@@ -349,6 +368,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
                 cols_next[it] = nt > 0 ? __ldg(idx_ptr + it * C::KPI) : 0;
                 if (TSP_CHECKED && (unsigned)cols_next[it] >= (unsigned)bounds.colA) { atomicExch(err, 0x20); cols_next[it] = 0; }
             }
+            const unsigned long long pol_keep = policy_evict_last();
             auto publish = [&](int i) {  // the B rows of tile i are complete in shared memory
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
@@ -362,7 +382,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
                 const unsigned st = ring + s * C::STAGE_BYTES;
 #pragma unroll
                 for (int it = 0; it < C::B_ITERS; it++)
-                    cp_async16(st + dst_off[it], gsrc + (unsigned long long)(unsigned)cols_next[it] * ldb_b);
+                    cp_async16_hint(st + dst_off[it], gsrc + (unsigned long long)(unsigned)cols_next[it] * ldb_b, pol_keep);
                 cp_async_commit();
                 idx_ptr += C::BNK;
                 if (i + 1 < nt)
@@ -419,7 +439,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
                                 asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"l"(crow + c0 + q), "f"(__uint_as_float(r[q])),
                                              "f"(__uint_as_float(r[q + 1])), "f"(__uint_as_float(r[q + 2])), "f"(__uint_as_float(r[q + 3])) : "memory");
                             else
-                                *reinterpret_cast<uint4 *>(crow + c0 + q) = make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]);
+                                __stcs(reinterpret_cast<uint4 *>(crow + c0 + q), make_uint4(r[q], r[q + 1], r[q + 2], r[q + 3]));
                         }
                     }
                 }
@@ -439,11 +459,12 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
             w = __shfl_sync(0xffffffffu, rw, 0);
             w_end = __shfl_sync(0xffffffffu, rw, 1) & 0x7fffffffu;
         };
+        const unsigned long long pol_once = policy_evict_first();
         auto fetch_record = [&](unsigned w, unsigned w_end, int slot) {   // packed record -> private buffer (cp.async, caller commits)
             if (w >> 31) return;                                         // dense records go straight into the ring slot
             const unsigned chunks = min(w_end - w, (unsigned)C::REC_CHUNKS);
             const unsigned char *src = pack + (size_t)w * 16;
-            for (unsigned q = lane; q < chunks; q += 32) cp_async16(my_recs + (unsigned)slot * C::REC_BYTES + q * 16, src + (size_t)q * 16);
+            for (unsigned q = lane; q < chunks; q += 32) cp_async16_hint(my_recs + (unsigned)slot * C::REC_BYTES + q * 16, src + (size_t)q * 16, pol_once);
         };
         if (nte > 0) { load_words(e, w_cur, w_cur_end); fetch_record(w_cur, w_cur_end, 0); }
         cp_async_commit();

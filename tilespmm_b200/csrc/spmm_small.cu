@@ -30,6 +30,28 @@ __device__ __forceinline__ void cp_async16s(unsigned smem, const void *gmem)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem), "l"(gmem));
 }
+// The same copy with an L2 eviction policy.  B is re-read many times per product and by every later product, while a
+// tile of A and a row of C pass through once per product: with B about the size of the L2, letting the one-pass data
+// go first keeps most of B resident (policies made once per thread with createpolicy).
+__device__ __forceinline__ void cp_async16_hint(unsigned smem, const void *gmem, unsigned long long policy)
+{
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "l"(policy));
+}
+__device__ __forceinline__ unsigned long long policy_evict_first()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long policy_evict_last()
+{
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void store_streaming(float4 *p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ void store_streaming(float2 *p, float2 v) { __stcs(p, v); }
+__device__ __forceinline__ void store_streaming(float *p, float v) { __stcs(p, v); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -195,6 +217,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     const unsigned char *a_tile = tile_val + (size_t)t0 * Cfg::A_BYTES;
     const unsigned char *grow = dB + stripe_bytes;
 
+    const unsigned long long pol_once = policy_evict_first(), pol_keep = policy_evict_last();
     auto issue = [&](int i) {
         const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
         if (BULK)
@@ -208,7 +231,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         }
         else
         {
-            if (lane * 16 < Cfg::A_BYTES) cp_async16s(st + lane * 16, a_src);
+            if (lane * 16 < Cfg::A_BYTES) cp_async16_hint(st + lane * 16, a_src, pol_once);
             a_src += TS * Cfg::A_BYTES;
             const int idx_mine = idx_next;
 #pragma unroll
@@ -216,7 +239,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 const int k = it * KPI + k_mine;
                 const int col = __shfl_sync(0xffffffffu, idx_mine, k);
-                cp_async16s(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b);
+                cp_async16_hint(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b, pol_keep);
             }
         }
         idx_ptr += TS * BN;
@@ -367,7 +390,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
                 {
                     const float v0 = acc[q][half * 2 + j], v1 = acc[q + 1][half * 2 + j], v2 = acc[q + 2][half * 2 + j], v3 = acc[q + 3][half * 2 + j];
                     if (split) { atomicAdd(p + q, v0); atomicAdd(p + q + 1, v1); atomicAdd(p + q + 2, v2); atomicAdd(p + q + 3, v3); }
-                    else *reinterpret_cast<float4 *>(p + q) = make_float4(v0, v1, v2, v3);
+                    else store_streaming(reinterpret_cast<float4 *>(p + q), make_float4(v0, v1, v2, v3));
                 }
             }
     }
@@ -385,8 +408,8 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             }
             else
             {
-                *reinterpret_cast<float2 *>(p0) = make_float2(acc[nb][0], acc[nb][1]);
-                *reinterpret_cast<float2 *>(p1) = make_float2(acc[nb][2], acc[nb][3]);
+                store_streaming(reinterpret_cast<float2 *>(p0), make_float2(acc[nb][0], acc[nb][1]));
+                store_streaming(reinterpret_cast<float2 *>(p1), make_float2(acc[nb][2], acc[nb][3]));
             }
         }
     }
@@ -404,7 +427,7 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 const float v0 = acc[q][j], v1 = acc[q][2 + j], v2 = acc[q + 1][j], v3 = acc[q + 1][2 + j];
                 if (split) { atomicAdd(p + 2 * q, v0); atomicAdd(p + 2 * q + 1, v1); atomicAdd(p + 2 * q + 2, v2); atomicAdd(p + 2 * q + 3, v3); }
-                else *reinterpret_cast<float4 *>(p + 2 * q) = make_float4(v0, v1, v2, v3);
+                else store_streaming(reinterpret_cast<float4 *>(p + 2 * q), make_float4(v0, v1, v2, v3));
             }
         }
     }
@@ -423,8 +446,8 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             }
             else
             {
-                p[0] = acc[mb][0]; p[ldc] = acc[mb][1];
-                p[8] = acc[mb][2]; p[ldc + 8] = acc[mb][3];
+                store_streaming(p, acc[mb][0]); store_streaming(p + ldc, acc[mb][1]);
+                store_streaming(p + 8, acc[mb][2]); store_streaming(p + ldc + 8, acc[mb][3]);
             }
         }
     }

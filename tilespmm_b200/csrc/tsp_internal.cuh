@@ -146,7 +146,7 @@ struct TspClass
     std::vector<int> h_tile_ptr, h_panel_row;
     // schedule for the current threshold
     int TH = 0, ntasks = 0, nsplit = 0;
-    long long cap_tasks = 0;
+    long long cap_tasks = 0, cap_panels = 0;   // capacities of the task arrays / the per-panel arrays (kept across conversions)
     unsigned int *d_task_row = nullptr;
     int *d_task_start = nullptr, *d_split_row = nullptr, *d_task_count = nullptr;
     // the same tasks as {row word, first tile, end tile, 0}, longest first (what the 16/8-row kernels walk)
@@ -169,6 +169,7 @@ struct tsp_handle
     int *d_error = nullptr;           // device-side error flag (bounded waits)
     // all tile arrays of the three classes live in two allocations (the second holds the packed 64-row records)
     void *tile_block = nullptr, *pack_block = nullptr;
+    size_t tile_block_bytes = 0, pack_block_bytes = 0;   // capacities: a later conversion that fits reuses the allocation
     // conversion workspace: chunks of device memory reused by every conversion of this handle, and a small pinned
     // host buffer for the few scalars a conversion reads back
     std::vector<std::pair<void *, size_t>> ws_chunks;
@@ -192,7 +193,8 @@ struct tsp_handle
 // rowptr/colidx/val are device pointers, or host pointers when csr_on_host (uploaded into the conversion workspace)
 int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz, const int *rowptr, const int *colidx, const void *val,
                      bool csr_on_host, float gamma, float delta, int shard_index, int shard_count);
-void tsp_free_tiles(tsp_handle *h);
+// forgets the converted matrix; release = false keeps the device allocations for the next conversion
+void tsp_free_tiles(tsp_handle *h, bool release = false);
 int tsp_export_values_upstream(const tsp_handle *h, int cls, void *h_dst);
 // one allocation for the tile arrays of all classes (sizes from cls[k].tilem / tilenum), zero-filled where needed
 int tsp_alloc_tile_arrays(tsp_handle *h);
