@@ -31,7 +31,7 @@
 namespace
 {
 
-constexpr int CHAIN_L = 512;  // 8-row blocks per chunk of the chain resolution
+constexpr int CHAIN_L = 64;   // 8-row blocks per chunk of the chain resolution
 
 // Bump allocator over the handle's workspace chunks.  The first conversion sizes chunk 0 from nnz and rowA; what
 // does not fit (sizes known only later) goes into further chunks, which later conversions reuse.
@@ -226,51 +226,133 @@ __global__ void k_decide(int nb8, int rowA, float gamma, float delta, int fixed,
 
 __device__ __forceinline__ int step_of(int cls) { return cls == 0 ? 8 : (cls == 1 ? 2 : 1); }
 
+// The greedy chain i <- i + step(i) is resolved chunk-wise.  Chunks are short (CHAIN_L blocks) and staged in shared
+// memory, so that a walk costs shared-memory latency per step; the chunks are then linked by a parallel scan over
+// "entry offset -> exit offset" tables (8 states), not by a serial pass.
+
 // For every chunk of CHAIN_L blocks and every entry offset 0..7: where the chain leaves the chunk and how
-// many panels of each class it creates inside.
-__global__ void k_chain_local(int nb8, int nchunk, const unsigned char *__restrict__ cls_of, unsigned char *__restrict__ exit_off,
-                              int *__restrict__ counts /* [nchunk*8][3] */)
+// many panels of each class it creates inside.  One thread per (chunk, entry); 32 chunks per block of 256 threads.
+__global__ void __launch_bounds__(256)
+k_chain_local(int nb8, int nchunk, const unsigned char *__restrict__ cls_of, unsigned char *__restrict__ exit_off,
+              int *__restrict__ counts /* [nchunk*8][3] */)
 {
-    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    __shared__ unsigned char cls_s[32 * CHAIN_L];
+    const long long first = (long long)blockIdx.x * 32 * CHAIN_L;
+    for (int i = threadIdx.x; i < 32 * CHAIN_L; i += 256) cls_s[i] = first + i < nb8 ? cls_of[first + i] : 2;
+    __syncthreads();
+    const int t = blockIdx.x * 256 + threadIdx.x;
     if (t >= nchunk * 8) return;
-    const int c = t >> 3, o = t & 7;
-    long long pos = (long long)c * CHAIN_L + o;
-    const long long end = min((long long)(c + 1) * CHAIN_L, (long long)nb8);
-    int cnt[3] = {0, 0, 0};
-    while (pos < end)
+    const int c = t >> 3, o = t & 7, lc = threadIdx.x >> 3;
+    const int len = (int)min((long long)CHAIN_L, (long long)nb8 - (long long)c * CHAIN_L);
+    int pos = o, cnt[3] = {0, 0, 0};
+    while (pos < len)
     {
-        const int k = cls_of[pos];
+        const int k = cls_s[lc * CHAIN_L + pos];
         cnt[k]++;
         pos += step_of(k);
     }
-    long long off = pos - (long long)(c + 1) * CHAIN_L;
+    const int off = pos - CHAIN_L;
     exit_off[t] = (unsigned char)(off < 0 ? 0 : (off > 7 ? 7 : off));
     counts[t * 3 + 0] = cnt[0]; counts[t * 3 + 1] = cnt[1]; counts[t * 3 + 2] = cnt[2];
 }
 
-// Sequential composition over chunks (one thread; nchunk is rows/4096).
-__global__ void k_chain_compose(int nchunk, const unsigned char *__restrict__ exit_off, const int *__restrict__ counts,
-                                int *__restrict__ entry, int *__restrict__ base /* [nchunk+1][3] */)
+// Links the chunks: the entry offset of every chunk (composition of the chunks' transition tables, 8 states of 3 bits
+// packed into one word) and the number of panels of each class before it.  One block; scans by composition.
+__global__ void __launch_bounds__(1024)
+k_chain_compose(int nchunk, const unsigned char *__restrict__ exit_off, const int *__restrict__ counts, int *__restrict__ entry,
+                int *__restrict__ base /* [nchunk+1][3] */)
 {
-    if (blockIdx.x || threadIdx.x) return;
-    int e = 0, run[3] = {0, 0, 0};
-    for (int c = 0; c < nchunk; c++)
+    __shared__ unsigned int warp_f[32];
+    __shared__ int warp_n[32][3];
+    __shared__ unsigned int carry_state;
+    __shared__ int carry_n[3];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // f(state) for all 8 states in one word; compose(f, g)(x) = g(f(x)) -- f first
+    auto apply = [](unsigned int f, unsigned int x) { return (f >> (3 * x)) & 7u; };
+    auto compose = [&](unsigned int f, unsigned int g) {
+        unsigned int h = 0;
+#pragma unroll
+        for (unsigned int x = 0; x < 8; x++) h |= apply(g, apply(f, x)) << (3 * x);
+        return h;
+    };
+    constexpr unsigned int IDENT = 0u | 1u << 3 | 2u << 6 | 3u << 9 | 4u << 12 | 5u << 15 | 6u << 18 | 7u << 21;
+    if (threadIdx.x == 0) { carry_state = 0; carry_n[0] = carry_n[1] = carry_n[2] = 0; }
+    __syncthreads();
+    for (int base_c = 0; base_c < nchunk; base_c += 1024)
     {
-        entry[c] = e;
-        base[c * 3 + 0] = run[0]; base[c * 3 + 1] = run[1]; base[c * 3 + 2] = run[2];
-        const int t = c * 8 + e;
-        run[0] += counts[t * 3 + 0]; run[1] += counts[t * 3 + 1]; run[2] += counts[t * 3 + 2];
-        e = exit_off[t];
+        const int c = base_c + threadIdx.x;
+        unsigned int f = IDENT;
+        if (c < nchunk)
+        {
+            f = 0;
+            for (unsigned int x = 0; x < 8; x++) f |= (unsigned int)exit_off[c * 8 + x] << (3 * x);
+        }
+        // inclusive scan of the transition tables over the 1024 chunks of this pass
+        unsigned int incl = f;
+        for (int o = 1; o < 32; o <<= 1) { const unsigned int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl = compose(y, incl); }
+        if (lane == 31) warp_f[warp] = incl;
+        __syncthreads();
+        if (warp == 0)
+        {
+            unsigned int w = warp_f[lane];
+            for (int o = 1; o < 32; o <<= 1) { const unsigned int y = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w = compose(y, w); }
+            warp_f[lane] = w;
+        }
+        __syncthreads();
+        // exclusive prefix function of this chunk: everything before it in this pass
+        unsigned int excl = __shfl_up_sync(0xffffffffu, incl, 1);
+        if (lane == 0) excl = IDENT;
+        if (warp > 0) excl = compose(warp_f[warp - 1], excl);
+        const unsigned int e = apply(excl, carry_state);       // the true entry offset of chunk c
+        int n[3] = {0, 0, 0};
+        if (c < nchunk)
+        {
+            entry[c] = (int)e;
+            const int t = c * 8 + (int)e;
+            n[0] = counts[t * 3 + 0]; n[1] = counts[t * 3 + 1]; n[2] = counts[t * 3 + 2];
+        }
+        // exclusive prefix sums of the panel counts along the true path
+        int in[3] = {n[0], n[1], n[2]};
+        for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+            for (int k = 0; k < 3; k++) { const int y = __shfl_up_sync(0xffffffffu, in[k], o); if (lane >= o) in[k] += y; }
+        if (lane == 31) { warp_n[warp][0] = in[0]; warp_n[warp][1] = in[1]; warp_n[warp][2] = in[2]; }
+        __syncthreads();
+        if (warp == 0)
+        {
+            int w[3] = {warp_n[lane][0], warp_n[lane][1], warp_n[lane][2]};
+            for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+                for (int k = 0; k < 3; k++) { const int y = __shfl_up_sync(0xffffffffu, w[k], o); if (lane >= o) w[k] += y; }
+            warp_n[lane][0] = w[0]; warp_n[lane][1] = w[1]; warp_n[lane][2] = w[2];
+        }
+        __syncthreads();
+        if (c < nchunk)
+#pragma unroll
+            for (int k = 0; k < 3; k++) base[c * 3 + k] = carry_n[k] + (warp ? warp_n[warp - 1][k] : 0) + in[k] - n[k];
+        __syncthreads();
+        if (threadIdx.x == 1023)   // totals of this pass -> carry for the next
+        {
+            carry_state = apply(compose(excl, f), carry_state);
+#pragma unroll
+            for (int k = 0; k < 3; k++) carry_n[k] += warp_n[31][k];
+        }
+        __syncthreads();
     }
-    base[nchunk * 3 + 0] = run[0]; base[nchunk * 3 + 1] = run[1]; base[nchunk * 3 + 2] = run[2];
+    if (threadIdx.x == 0) { base[nchunk * 3 + 0] = carry_n[0]; base[nchunk * 3 + 1] = carry_n[1]; base[nchunk * 3 + 2] = carry_n[2]; }
 }
 
-// Walk every chunk from its true entry and emit the panels in scan order.
-__global__ void k_chain_emit(int nb8, int nchunk, int rowA, const unsigned char *__restrict__ cls_of, const int *__restrict__ entry,
-                             const int *__restrict__ base, const int *__restrict__ rowptr, int *__restrict__ seq_blk,
-                             unsigned char *__restrict__ seq_cls, int *__restrict__ seq_idx, int *__restrict__ blk_seq,
-                             unsigned long long *__restrict__ class_rows_nnz /* [3][2] */)
+// Walk every chunk from its true entry and emit the panels in scan order.  One thread per chunk, 128 chunks per block.
+__global__ void __launch_bounds__(128)
+k_chain_emit(int nb8, int nchunk, int rowA, const unsigned char *__restrict__ cls_of, const int *__restrict__ entry,
+             const int *__restrict__ base, const int *__restrict__ rowptr, int *__restrict__ seq_blk,
+             unsigned char *__restrict__ seq_cls, int *__restrict__ seq_idx, int *__restrict__ blk_seq,
+             unsigned long long *__restrict__ class_rows_nnz /* [3][2] */)
 {
+    __shared__ unsigned char cls_s[128 * CHAIN_L];
+    const long long first = (long long)blockIdx.x * 128 * CHAIN_L;
+    for (int i = threadIdx.x; i < 128 * CHAIN_L; i += 128) cls_s[i] = first + i < nb8 ? cls_of[first + i] : 2;
+    __syncthreads();
     int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= nchunk) return;
     long long pos = (long long)c * CHAIN_L + entry[c];
@@ -280,7 +362,7 @@ __global__ void k_chain_emit(int nb8, int nchunk, int rowA, const unsigned char 
     unsigned long long rows[3] = {0, 0, 0}, nnz[3] = {0, 0, 0};
     while (pos < end)
     {
-        const int k = cls_of[pos], st = step_of(k);
+        const int k = cls_s[pos - first], st = step_of(k);
         seq_blk[seq] = (int)pos;
         seq_cls[seq] = (unsigned char)k;
         seq_idx[seq] = idx[k]++;
@@ -971,8 +1053,8 @@ int tsp_convert_impl(tsp_handle *h, int rowA, int colA, long long nnz64, const i
     }
     mark("stage 2 window counts");
     k_decide<<<blocks_for(nb8, T), T, 0, st>>>(nb8, rowA, gamma, delta, fixed, u8_ptr, n16, n64, cls_of);
-    k_chain_local<<<blocks_for((long long)nchunk * 8, T), T, 0, st>>>(nb8, nchunk, cls_of, exit_off, counts);
-    k_chain_compose<<<1, 32, 0, st>>>(nchunk, exit_off, counts, entry, base);
+    k_chain_local<<<blocks_for((long long)nchunk * 8, 256), 256, 0, st>>>(nb8, nchunk, cls_of, exit_off, counts);
+    k_chain_compose<<<1, 1024, 0, st>>>(nchunk, exit_off, counts, entry, base);
     k_chain_emit<<<blocks_for(nchunk, 128), 128, 0, st>>>(nb8, nchunk, rowA, cls_of, entry, base, d_rowptr, seq_blk, seq_cls, seq_idx, blk_seq,
                                                         class_rows_nnz);
     TSP_CUDA(cudaGetLastError());
