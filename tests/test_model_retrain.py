@@ -158,3 +158,20 @@ def test_c_walker_reproduces_upstream_on_upstreams_own_table():
         assert rc == 0 and (g.value, d.value) == (np.float32(rec["gamma"]), np.float32(rec["delta"])), rec
         answers.add((g.value, d.value))
     assert len(answers) >= 5                                                            # not a constant function
+
+
+@pytest.mark.gpu
+def test_sweep_leg_times_candidates_on_the_gpu_and_the_fit_consumes_its_records(tmp_path):
+    """The measuring half of the refit: two small corpus cases, four candidates (one per class mix), real conversions,
+    tuning and timed loops on the GPU; the records it writes are what `fit` reads."""
+    out = tmp_path / "sweep.jsonl"
+    picks = [rm.CANDIDATES.index(c) for c in ((0.0, 1.5), (5.0, 0.0), (5.0, 3.0), (2.0, 1.2))]
+    rm.sweep(str(out), iters=5, cases={"fixed_4096x16", "stencil_32"}, candidates=picks)
+    recs = [json.loads(l) for l in open(out)]
+    assert [r["name"] for r in recs] == ["fixed_4096x16", "stencil_32"]
+    for r in recs:
+        assert len(r["ms"]) == len(rm.CANDIDATES) and all(t > 0 for t in r["ms"]) and len(r["features"]) == 11
+        assert len({r["ms"][i] for i in picks}) >= 2                 # different tilings were really timed
+    table = tmp_path / "table.inc"
+    trees = rm.fit([str(out)], depth=2, table_path=str(table))
+    assert set(trees) == {0, 1} and "kPolicyNodes" in table.read_text()

@@ -35,7 +35,8 @@
 namespace
 {
 
-constexpr unsigned WAIT_LIMIT = 1u << 22;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+constexpr unsigned WAIT_PARK_NS = 2000;
 #ifndef TSP64_NE
 #define TSP64_NE 2                     // expander warps
 #endif
@@ -148,14 +149,16 @@ __device__ __forceinline__ void tma_gather4(unsigned dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
-// bounded wait: false when the phase did not complete within WAIT_LIMIT polls
+// bounded wait: false when the phase did not complete within WAIT_LIMIT polls.  Every poll may park the thread for up to
+// WAIT_PARK_NS (the hardware wakes it when the phase completes), so a waiting thread issues few instructions and the
+// whole wait is bounded by about WAIT_LIMIT * WAIT_PARK_NS = 2 s.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity)
 {
     for (unsigned it = 0; it < WAIT_LIMIT; it++)
     {
         unsigned done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(done) : "r"(bar), "r"(parity), "r"(WAIT_PARK_NS) : "memory");
         if (done) return true;
     }
     return false;

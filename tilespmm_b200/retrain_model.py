@@ -63,14 +63,28 @@ def corpus():
     c.append(("mixed_262144_d50", lambda: synth.mixed_density(262144, seed=39, dense_fraction=0.5), 0, 128))
     c.append(("mixed_131072_d90", lambda: synth.mixed_density(131072, seed=40, dense_fraction=0.9, blocks_per_panel=8), 1, 128))
     c.append(("mixed_131072_dense_fp16", lambda: synth.mixed_density(131072, seed=41, dense_fraction=0.9, blocks_per_panel=8, density=0.9), 0, 64))
+    # banded and block-diagonal structure (rows that share their columns), more dense widths
+    c.append(("banded_131072_hb12", lambda: synth.banded(131072, 12, 0.6, seed=42), 1, 128))
+    c.append(("banded_131072_hb40_fp16", lambda: synth.banded(131072, 40, 0.5, seed=43), 0, 64))
+    c.append(("banded_262144_hb4", lambda: synth.banded(262144, 4, 0.9, seed=44), 1, 32))
+    c.append(("blockdiag_65536_b64", lambda: synth.block_diagonal(65536, 64, 0.3, seed=45), 1, 256))
+    c.append(("blockdiag_131072_b32_fp16", lambda: synth.block_diagonal(131072, 32, 0.5, seed=46), 0, 128))
+    c.append(("blockdiag_32768_b128", lambda: synth.block_diagonal(32768, 128, 0.15, seed=47), 1, 64))
+    c.append(("stencil_40_c32", lambda: synth.stencil27(40, seed=48), 1, 32))
+    c.append(("rmat_17_fp16_c256", lambda: synth.rmat_symmetric(17, seed=49), 0, 256))
     return c
 
 
-def sweep(out_path: str, iters: int):
+def sweep(out_path: str, iters: int, cases=None, candidates=None):
+    """Times the candidates on the corpus.  `cases` (names) and `candidates` (indices into CANDIDATES) restrict the sweep;
+    a candidate that is not timed gets the time of the default pair."""
     import torch
     from . import api, synth
+    picked = set(range(len(CANDIDATES))) if candidates is None else set(candidates) | {DEFAULT_LEAF}
     with open(out_path, "w") as out:
         for name, gen, prec, colB in corpus():
+            if cases is not None and name not in cases:
+                continue
             rp, ci, v, shape = gen()
             cb = api.padded_width(colB)
             B = synth.dense_b(shape[1], cb, 1, "uniform")
@@ -83,7 +97,10 @@ def sweep(out_path: str, iters: int):
             m = api.TileMatrix(prec)
             seen, times = {}, []
             t_case = time.perf_counter()
-            for (g, d) in CANDIDATES:
+            for index, (g, d) in enumerate(CANDIDATES):
+                if index not in picked:
+                    times.append(None)
+                    continue
                 m.convert_device(shape, d_rp, d_ci, d_v, ci.size, g, d)
                 info = m.info()
                 key = tuple(int(x) for x in info[:, [0, 3]].ravel())   # rows and tiles per class
@@ -93,6 +110,7 @@ def sweep(out_path: str, iters: int):
                     seen[key] = m.time(dB, dC, cb, iters)
                     del dC
                 times.append(seen[key])
+            times = [t if t is not None else times[DEFAULT_LEAF] for t in times]
             m.close()
             rec = {"name": name, "precision": prec, "colB": colB, "features": [float(x) for x in feats], "ms": times}
             out.write(json.dumps(rec) + "\n")
@@ -120,8 +138,10 @@ def _best_leaf(cases):
     return best, float(tot[best])
 
 
-def grow(cases, depth, min_gain=0.02):
-    """Binary tree as nested tuples: ("leaf", index) or ("node", feature, cut, left, right); value < cut goes left."""
+def grow(cases, depth, min_gain=0.005, min_leaf=2):
+    """Binary tree as nested tuples: ("leaf", index) or ("node", feature, cut, left, right); value < cut goes left.
+    A split must buy `min_gain` of mean regret and leave at least `min_leaf` cases on either side: one matrix is no
+    evidence for a rule."""
     leaf, cost = _best_leaf(cases)
     if depth == 0 or len(cases) < 2:
         return ("leaf", leaf), cost
@@ -132,15 +152,15 @@ def grow(cases, depth, min_gain=0.02):
             cut = np.float32((float(lo) + float(hi)) / 2)
             left = [c for c in cases if np.float32(c["features"][f + 2]) < cut]
             right = [c for c in cases if not np.float32(c["features"][f + 2]) < cut]
-            if not left or not right:
+            if len(left) < min_leaf or len(right) < min_leaf:
                 continue
             cl = _best_leaf(left)[1] + _best_leaf(right)[1]
             if best is None or cl < best[0]:
                 best = (cl, f, float(cut), left, right)
-    if best is None or best[0] > cost - min_gain * len(cases):     # a split must buy 2 % mean regret
+    if best is None or best[0] > cost - min_gain * len(cases):     # a split must buy min_gain of mean regret
         return ("leaf", leaf), cost
-    lt, lc = grow(best[3], depth - 1, min_gain)
-    rt, rc = grow(best[4], depth - 1, min_gain)
+    lt, lc = grow(best[3], depth - 1, min_gain, min_leaf)
+    rt, rc = grow(best[4], depth - 1, min_gain, min_leaf)
     if lc + rc > cost - min_gain * len(cases):
         return ("leaf", leaf), cost
     return ("node", best[1], best[2], lt, rt), lc + rc

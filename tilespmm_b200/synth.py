@@ -154,6 +154,36 @@ def mixed_density(n: int = 524288, seed: int = 1004, dense_fraction: float = 0.1
     return np.cumsum(rowptr).astype(np.int32), cols.astype(np.int32), vals, (n, n)
 
 
+def banded(n: int = 65536, half_bandwidth: int = 12, fill: float = 0.6, seed: int = 1006):
+    """Banded matrix: every row holds a random `fill` share of the 2*half_bandwidth+1 diagonals around the main one
+    (the diagonal itself always); values N(0, 1).  Neighbouring rows share almost all their columns."""
+    rng = _rng(seed)
+    offs = np.arange(-half_bandwidth, half_bandwidth + 1, dtype=np.int64)
+    keep = rng.random((n, offs.size), dtype=np.float32) < fill
+    keep[:, half_bandwidth] = True
+    rows = np.repeat(np.arange(n, dtype=np.int64), offs.size).reshape(n, offs.size)
+    cols = rows + offs[None, :]
+    ok = keep & (cols >= 0) & (cols < n)
+    r, c = rows[ok], cols[ok]
+    rowptr = np.zeros(n + 1, dtype=np.int64)
+    np.add.at(rowptr, r + 1, 1)
+    vals = rng.standard_normal(r.size, dtype=np.float32)
+    return np.cumsum(rowptr).astype(np.int32), c.astype(np.int32), vals, (n, n)
+
+
+def block_diagonal(n: int = 65536, block: int = 64, density: float = 0.3, seed: int = 1007):
+    """Block-diagonal matrix: dense-ish `block` x `block` blocks of the given density on the diagonal; values N(0, 1)."""
+    rng = _rng(seed)
+    nb = n // block
+    mask = rng.random((nb, block, block), dtype=np.float32) < density
+    bi, ri, ci = np.nonzero(mask)
+    r, c = bi.astype(np.int64) * block + ri, bi.astype(np.int64) * block + ci
+    rowptr = np.zeros(n + 1, dtype=np.int64)
+    np.add.at(rowptr, r + 1, 1)
+    vals = rng.standard_normal(r.size, dtype=np.float32)
+    return np.cumsum(rowptr).astype(np.int32), c.astype(np.int32), vals, (n, n)
+
+
 def dense_b(rows: int, cols: int, seed: int, dist: str = "uniform") -> np.ndarray:
     """Dense right-hand side, row-major float32: U[-1, 1] ("uniform") or N(0, 1) ("normal")."""
     rng = _rng(seed + 7919)
