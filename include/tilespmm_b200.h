@@ -91,6 +91,10 @@ int tsp_top4(const tsp_handle *h, int cls, int colB_padded, int *top4);
  * prints per kernel (pre/prefetch_probe.cu:12-28): out6 = {threads per block, registers per thread, shared bytes
  * per block, bytes fetched per pipeline step of a block, tasks per block, column stripes per task}. */
 int tsp_kernel_info(const tsp_handle *h, int cls, int colB_padded, long long *out6);
+/* The weight of one atomic slice that tsp_top4 uses for (precision, cls, colB_padded): the platform calibration that
+ * upstream hard-codes as the lambda_atom table of get_optimal_prefetch_th (src/csr2tile.h:483-495), here fitted to
+ * these kernels on B200 (tilespmm_b200/calibrate_atom.py writes csrc/atom_table.inc). */
+float tsp_atom_weight(int precision, int cls, int colB_padded);
 /* upstream tile_pretreatment + update_metadata (src/csr2tile.h:383-434, 644-711): builds the task arrays of
  * class cls for threshold TH on the device. */
 int tsp_schedule(tsp_handle *h, int cls, int TH);

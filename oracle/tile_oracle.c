@@ -359,6 +359,9 @@ typedef struct
      * 4 tasks per block for the 32-column 8/16-row kernels, else 1; ceil(colB/64) stripes, 1 when colB == 32
      * (src/csr2tile.h:590-601). */
     int tasks_per_block, stripes;
+    /* weight of one atomic slice.  Upstream hard-codes a table "calibrated from existing platform data"
+     * (src/csr2tile.h:483-495); 0 selects that table, any other value stands in for a platform's own calibration. */
+    float atom_weight;
 } OrcResources;
 
 /* Upstream get_optimal_prefetch_th (src/csr2tile.h:437-642); float arithmetic in upstream's order. */
@@ -390,6 +393,7 @@ int orc_top4(const OrcTiles *T, int cls, int colB, const OrcResources *R, int *t
         if (BM == 16) lambda_atom = is_tf32 ? 0.01048f : 0.01163f;
         else if (BM == 8) lambda_atom = is_tf32 ? 0.00960f : 0.00826f;
     }
+    if (R->atom_weight != 0.0f) lambda_atom = R->atom_weight;
     float atom_per_col = lambda_atom * (1.0f / 32.0f);
 
     int max_len = 0;

@@ -34,7 +34,8 @@ class OrcResources(C.Structure):
     _fields_ = [("sm_count", C.c_int), ("threads_per_sm", C.c_int), ("blocks_per_sm", C.c_int),
                 ("registers_per_sm", C.c_int), ("l2_bytes", C.c_int), ("shared_bytes_per_sm", C.c_longlong),
                 ("threads", C.c_int), ("registers_per_thread", C.c_int), ("iteration_bytes", C.c_int),
-                ("shared_bytes", C.c_longlong), ("tasks_per_block", C.c_int), ("stripes", C.c_int)]
+                ("shared_bytes", C.c_longlong), ("tasks_per_block", C.c_int), ("stripes", C.c_int),
+                ("atom_weight", C.c_float)]   # 0 = upstream's table
 
 
 # rows of the upstream kernel table compiled into oracle/_ref (oracle/make_prefetch_stub.sh):

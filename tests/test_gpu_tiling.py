@@ -55,7 +55,7 @@ def test_tiling_bit_exact_vs_upstream_golden(name, prec):
 
 @pytest.mark.parametrize("prec", [0, 1])
 def test_threshold_candidates_match_cost_model(prec):
-    """tsp_top4 against the checker's cost model fed with the resource rows of THESE kernels."""
+    """tsp_top4 against the checker's cost model fed with the resource rows and the atomic weight of THESE kernels."""
     from tilespmm_b200 import api
     import torch
     props = torch.cuda.get_device_properties(0)
@@ -69,7 +69,8 @@ def test_threshold_candidates_match_cost_model(prec):
                     k = m.kernel_info(cls, cb)
                     res = _orc.OrcResources(props.multi_processor_count, props.max_threads_per_multi_processor, 32,
                                             props.regs_per_multiprocessor, props.L2_cache_size, props.shared_memory_per_multiprocessor,
-                                            int(k[0]), int(k[1]), int(k[3]), int(k[2]), int(k[4]), int(k[5]))
+                                            int(k[0]), int(k[1]), int(k[3]), int(k[2]), int(k[4]), int(k[5]),
+                                            api.atom_weight(prec, cls, cb))
                     assert m.top4(cls, cb).tolist() == o.top4(cls, cb, res).tolist(), (name, g, d, cls, cb)
             m.close()
 

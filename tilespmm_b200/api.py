@@ -39,6 +39,8 @@ def lib() -> C.CDLL:
         L.tsp_info.argtypes = [vp, vp, vp]
         L.tsp_export.argtypes = [vp, i, i, vp, C.POINTER(ll)]
         L.tsp_top4.argtypes = [vp, i, i, vp]
+        L.tsp_atom_weight.argtypes = [i, i, i]
+        L.tsp_atom_weight.restype = C.c_float
         L.tsp_kernel_info.argtypes = [vp, i, i, vp]
         L.tsp_schedule.argtypes = [vp, i, i]
         L.tsp_export_schedule.argtypes = [vp, i, C.POINTER(i), vp, vp]
@@ -99,6 +101,11 @@ def features_from_csr(rowptr, shape, capability: float, colB: int) -> np.ndarray
     if not lib().tsp_features_from_csr(shape[0], shape[1], int(rowptr[-1]), _p(rowptr), capability, colB, _p(f)):
         raise TileSpMMError("inconsistent CSR row pointer")
     return f
+
+
+def atom_weight(precision: int, cls: int, colB_padded: int) -> float:
+    """Weight of one atomic slice in the threshold cost model (tsp_atom_weight)."""
+    return float(lib().tsp_atom_weight(precision, cls, colB_padded))
 
 
 def predict(precision: int, features) -> tuple[float, float]:

@@ -25,7 +25,7 @@ def _newer(target: str, deps: list[str]) -> bool:
 def _compile_and_link(lib: str, objdir: str, extra_flags: list[str], force: bool):
     nvcc = os.environ.get("NVCC", "nvcc")
     headers = [os.path.join(CSRC, "tsp_internal.cuh"), os.path.join(HERE, "..", "include", "tilespmm_b200.h"),
-               os.path.join(CSRC, "model_table.inc")]
+               os.path.join(CSRC, "model_table.inc"), os.path.join(CSRC, "atom_table.inc")]
     objs = []
     os.makedirs(objdir, exist_ok=True)
     procs = []
@@ -56,7 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     path of the release library."""
     nvcc = os.environ.get("NVCC", "nvcc")
     headers = [os.path.join(CSRC, "tsp_internal.cuh"), os.path.join(HERE, "..", "include", "tilespmm_b200.h"),
-               os.path.join(CSRC, "model_table.inc")]
+               os.path.join(CSRC, "model_table.inc"), os.path.join(CSRC, "atom_table.inc")]
     logs = _compile_and_link(LIB, os.path.join(HERE, "build"), [], force)
     _compile_and_link(LIB_DEBUG, os.path.join(HERE, "build", "debug"), ["-DTSP_DEBUG=1"], force)
     # the two drop-in executables (upstream bin/tilespmm_fp16, bin/tilespmm_tf32)

@@ -175,6 +175,17 @@ int tsp_export_schedule(const tsp_handle *h, int cls, int *ntasks, unsigned int 
     return TSP_OK;
 }
 
+#include "atom_table.inc"
+
+// Weight of one atomic slice in the cost model below: upstream's table has this shape (one row for 32 columns, one for
+// wider right-hand sides, src/csr2tile.h:483-495) but holds constants fitted to its kernels on its GPUs; the values
+// here are fitted to these kernels on B200 by tilespmm_b200/calibrate_atom.py.
+float tsp_atom_weight(int precision, int cls, int colB_padded)
+{
+    if (cls < 0 || cls > 2) return 0.01f;
+    return kAtomWeight[colB_padded == 32 ? 0 : 1][cls][precision ? 1 : 0];
+}
+
 // The four cheapest thresholds under the upstream cost model (src/csr2tile.h:437-642).
 int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
 {
@@ -196,19 +207,7 @@ int tsp_top4(const tsp_handle *h, int cls, int colB, int *top4)
     if (blk_sm <= 0) { tsp_set_error("top4: the kernel does not fit this GPU"); return TSP_EDEVICE; }
     const float cap = (float)(blk_sm * sm);
     const float lambda_l2 = (float)(R.iteration_bytes * cap) / (float)h->prop.l2CacheSize;
-    // weight of one atomic slice; the table is upstream's (src/csr2tile.h:484-495)
-    float lambda_atom = 0.01f;
-    if (colB == 32)
-    {
-        if (BM == 64) lambda_atom = is_tf32 ? 0.020f : 0.019f;
-        else if (BM == 16) lambda_atom = is_tf32 ? 0.00830f : 0.00844f;
-        else lambda_atom = is_tf32 ? 0.00674f : 0.00360f;
-    }
-    else
-    {
-        if (BM == 16) lambda_atom = is_tf32 ? 0.01048f : 0.01163f;
-        else if (BM == 8) lambda_atom = is_tf32 ? 0.00960f : 0.00826f;
-    }
+    const float lambda_atom = tsp_atom_weight(is_tf32, cls, colB);
     const float atom_per_col = lambda_atom * (1.0f / 32.0f);
 
     const std::vector<int> &tp = c.h_tile_ptr;

@@ -85,6 +85,11 @@ __device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, 
 #ifndef TSP_SMALL_BULK
 #define TSP_SMALL_BULK 0
 #endif
+// Resident CTAs per SM each instance is compiled for (the register budget of its launch bounds).  The 16-row kernels
+// keep 64 accumulator registers per lane at 128 columns: compiled for 5 or 6 CTAs they spill and measure 16 % / 90 %
+// slower on the 27-point stencil (TF32), and a third ring slot at 4 CTAs is 4 % slower than two -- the kernel is bound
+// by the shared-memory data path (72 % busy) and by issue latency at 16 warps per SM, not by bytes in flight.
+constexpr int small_ctas(int cls, int ns) { return cls == 2 ? (ns <= 64 ? 8 : 6) : 4; }
 // BULK: the gathered rows and the A tile are fetched by the bulk-copy engine (cp.async.bulk, one copy per row
 // segment, completion on an mbarrier per ring slot) instead of per-lane 16-byte cp.async through the load/store
 // path; rows then sit unswizzled in shared memory with a 16-byte pad per row to keep the operand loads conflict-free.
@@ -145,7 +150,7 @@ __device__ __forceinline__ int swz(int c, int k)
 // added up through shared memory.  Used for launches that would not fill the GPU with one warp per unit: the chain of
 // dependent tile fetches of a panel is four times shorter.
 template <int PREC, int CLS, int NS, bool COOP>
-__global__ void __launch_bounds__(WARPS * 32, (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4))
+__global__ void __launch_bounds__(WARPS * 32, small_ctas(CLS, NS))
 k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, const uint4 *__restrict__ task_pack,
              const int *__restrict__ tile_colidx, const unsigned char *__restrict__ tile_val,
              const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err, const TspBounds bounds)
@@ -473,7 +478,7 @@ int launch_one(tsp_handle *h, const void *d_b, float *d_c, int colB, cudaStream_
     TspRange range(CLS == 1 ? "tsp 16-row class kernel" : "tsp 8-row class kernel");
     // One warp per unit fills the GPU only when there are several units per resident warp slot; below that (small
     // matrices) a CTA per unit with the tiles dealt out to its four warps is faster.  Tasks of one or two tiles gain nothing.
-    const long long warp_slots = (long long)h->prop.multiProcessorCount * (CLS == 2 ? (NS <= 64 ? 8 : 6) : 4) * WARPS;
+    const long long warp_slots = (long long)h->prop.multiProcessorCount * small_ctas(CLS, NS) * WARPS;
     const bool coop = units * WARPS <= warp_slots && (long long)c.tilenum >= 3 * (long long)c.ntasks;
     const int grid = coop ? (int)units : (int)((units + WARPS - 1) / WARPS);
     (coop ? kern_coop : kern)<<<grid, WARPS * 32, Cfg::SMEM, s>>>(c.ntasks, nstripes, colB, h->row_begin, c.d_task_pack, c.d_tile_colidx,

@@ -72,6 +72,9 @@ struct CfgT
     static constexpr int IDXV = (G * BN + 31) / 32;        // registers per lane that hold a group's column indices
     static constexpr int TMEM_COLS = 32;                   // two accumulators of 16 columns
     static_assert(B_ITERS >= 1 && BN % KPI == 0, "producer mapping");
+    // tcgen05.alloc blocks until columns are free, so the CTAs that can be resident on an SM together (bounded by the
+    // 2048 threads of an SM) must never ask for more than the 512 columns of its tensor memory
+    static_assert((2048 / THREADS) * TMEM_COLS <= 512, "resident CTAs would oversubscribe tensor memory");
     // A parity wait on an mbarrier is only meaningful for a waiter that is neither two phases ahead of the barrier nor
     // two behind.  Every barrier here therefore has one waiting agent that takes each phase in turn: with R % PW == 0
     // and STAGES % PW == 0 a descriptor slot and a data slot always belong to the same producer warp (the MMA issuers
