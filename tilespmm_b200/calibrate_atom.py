@@ -64,7 +64,7 @@ def uniform_matrix(rows, per_row, seed):
     return rowptr, colidx, vals, (rows, rows)
 
 
-def fit_case(precision, cls, colB, iters=200, panels=8192, tiles_per_panel=64, seed=77):
+def fit_case(precision, cls, colB, iters=200, panels=4096, tiles_per_panel=128, seed=77, verbose=False):
     import torch
     from . import api
     bn = {0: (32, 16, 16), 1: (16, 8, 8)}[precision][cls]
@@ -92,6 +92,8 @@ def fit_case(precision, cls, colB, iters=200, panels=8192, tiles_per_panel=64, s
         t = min(m.time(dB, dC, cb, iters, cls) for _ in range(3))
         X.append([comp, extra * cb / 32.0])
         y.append(t)
+        if verbose:
+            print(f"    TH={TH} computation={comp:.1f} extra_slices={extra} ms={t:.5f}", flush=True)
     m.close()
     return fit_weight(X, y) + (len(y),)
 
@@ -126,7 +128,9 @@ def main(argv=None):
     ap.add_argument("--write", action="store_true", help="rewrite csrc/atom_table.inc with the fitted weights")
     ap.add_argument("--out", default=TABLE, help="where --write puts the table (default: csrc/atom_table.inc)")
     ap.add_argument("--iters", type=int, default=200)
-    ap.add_argument("--panels", type=int, default=8192)
+    ap.add_argument("--panels", type=int, default=4096)
+    ap.add_argument("--tiles-per-panel", type=int, default=128)
+    ap.add_argument("--verbose", action="store_true", help="print every timed threshold")
     args = ap.parse_args(argv)
     import torch
     if not torch.cuda.is_available():
@@ -136,7 +140,8 @@ def main(argv=None):
     for precision in (0, 1):
         for cls in (0, 1, 2):
             for wide, colB in ((0, 32), (1, 128)):
-                lam, raw, r2, n = fit_case(precision, cls, colB, iters=args.iters, panels=args.panels)
+                lam, raw, r2, n = fit_case(precision, cls, colB, iters=args.iters, panels=args.panels, tiles_per_panel=args.tiles_per_panel,
+                                           verbose=args.verbose)
                 w[(precision, cls, wide)] = lam
                 print(f"precision={precision} class={BM[cls]}-row colB={colB}: lambda_atom={lam:.5f} (unclamped {raw:.5f}, R2={r2:.3f}, {n} thresholds; "
                       f"library now {api_weight(precision, cls, colB):.5f})", flush=True)
