@@ -49,3 +49,14 @@ def test_cost_terms_agree_with_the_checker(prec, cls, cb, weight):
     top4 = o.top4(cls, cb, res).tolist()
     # near ties may swap under float32 rounding: the checker's first choice must be within 0.1 % of the minimum here
     assert costs[top4[0]] <= costs[best] * 1.001, (top4, best, costs)
+
+
+def test_library_table_is_within_the_accepted_range():
+    """tsp_atom_weight is a host-side table lookup: every entry lies in the range the calibration may write."""
+    from tilespmm_b200 import api
+    for prec in (0, 1):
+        for cls in (0, 1, 2):
+            for cb in (32, 64, 128, 256):
+                w = api.atom_weight(prec, cls, cb)
+                assert cal.LO * 0.999 <= w <= cal.HI * 1.001, (prec, cls, cb, w)
+            assert api.atom_weight(prec, cls, 64) == api.atom_weight(prec, cls, 256)   # one row for every width above 32
