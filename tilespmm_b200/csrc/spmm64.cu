@@ -14,7 +14,8 @@
 // the tile records and column indices are read once per 256 columns (upstream: once per 64).  Roles:
 //   warps 0..PW-1   B producers (PW = 8 for stripes of 128 columns and more, else 4).  Together they gather the B rows
 //              named by tile_colidx with 16-byte cp.async straight into the swizzled MN-major operand layout of the ring
-//              slot, every thread a fixed few chunks of every tile, and publish a tile LAG tiles after issuing it.  In the
+//              slot, every thread a fixed few chunks of every tile; nobody waits for the data (each thread leaves a
+//              cp.async.mbarrier.arrive on the slot's barrier), so every free slot is in flight.  In the
 //              TMA form one lane issues cp.async.bulk.tensor ... tile::gather4 requests instead.  What bounds a
 //              gather-fed kernel on this GPU is the number of independent warps that issue loads (a warp issues an
 //              instruction every ~11 cycles), which is why the rows of ONE tile are spread over all producer threads.
@@ -56,19 +57,13 @@ struct Cfg64
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int B_ITERS = (BNK * CPR) / (PW * 32);   // copies per producer thread per tile
     static constexpr int KPI = PW * 32 / CPR;                 // tile rows covered by one CTA-wide copy
-    // ring depth and how many tiles the producers run ahead of what they have published: a slot is reused
-    // STAGES tiles later, LAG+1 tiles are in flight to memory, and the MMA has STAGES-LAG tiles of slack
+    // ring depth: a slot is reused STAGES tiles later and all STAGES slots can be in flight to memory
 #ifdef TSP64_STAGES
     static constexpr int STAGES = TSP64_STAGES;
 #else
     static constexpr int STAGES = N >= 128 ? 4 : (N == 64 ? 6 : 8);
 #endif
-#ifdef TSP64_LAG
-    static constexpr int LAG = TSP64_LAG;
-#else
-    static constexpr int LAG = N >= 128 ? 2 : 4;
-#endif
-    static_assert(B_ITERS >= 1 && LAG < STAGES, "unsupported pipeline shape");
+    static_assert(B_ITERS >= 1, "unsupported pipeline shape");
     // packed records
     static constexpr int MASK_BYTES = 64 * BNK / 8;           // 128 (TF32) / 256 (FP16)
     static constexpr int REC_MAX_VALS = TSP_REC_MAX_VALS(PREC);
@@ -127,6 +122,11 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+// arrive on the mbarrier when every cp.async this thread has issued so far has landed; the thread itself does not wait
+__device__ __forceinline__ void cp_async_arrive(unsigned bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(unsigned bar)
 {
@@ -297,7 +297,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
     }
 
     // a slot is full when the B producers (PW warps, or the one TMA lane) and the tile's expander have arrived
-    constexpr unsigned FULL_COUNT = (TMA ? 1 : PW) + 1;
+    constexpr unsigned FULL_COUNT = (TMA ? 1 : PW * 32) + 1;
     if (tid == 0)
     {
         for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, FULL_COUNT); mbar_init(bar_empty + 8 * s, 1); }
@@ -372,12 +372,8 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
                 if (TSP_CHECKED && (unsigned)cols_next[it] >= (unsigned)bounds.colA) { atomicExch(err, 0x20); cols_next[it] = 0; }
             }
             const unsigned long long pol_keep = policy_evict_last();
-            auto publish = [&](int i) {  // the B rows of tile i are complete in shared memory
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full + 8 * (i % S));
-            };
-            int published = 0;
+            // Nobody waits for the copies: every thread leaves an arrival on the slot's barrier that is delivered when its own
+            // copies have landed, so every slot the MMA has released is in flight again at once.
             for (int i = 0; i < nt && ok; i++)
             {
                 const int s = i % S;
@@ -386,7 +382,7 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
 #pragma unroll
                 for (int it = 0; it < C::B_ITERS; it++)
                     cp_async16_hint(st + dst_off[it], gsrc + (unsigned long long)(unsigned)cols_next[it] * ldb_b, pol_keep);
-                cp_async_commit();
+                cp_async_arrive(bar_full + 8 * s);
                 idx_ptr += C::BNK;
                 if (i + 1 < nt)
                 {
@@ -397,16 +393,8 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
                         if (TSP_CHECKED && (unsigned)cols_next[it] >= (unsigned)bounds.colA) { atomicExch(err, 0x20); cols_next[it] = 0; }
                     }
                 }
-                if (i >= C::LAG)
-                {
-                    cp_async_wait<C::LAG>();  // the group of tile i-LAG has landed
-                    publish(i - C::LAG);
-                    published = i - C::LAG + 1;
-                }
             }
-            cp_async_wait<0>();
-            if (ok)
-                for (int i = published; i < nt; i++) publish(i);
+            asm volatile("cp.async.wait_all;\n" ::: "memory");   // no copy of this CTA outlives its shared memory
         }
 
         // ------------------------------------------------------------ epilogue (warps 0-3: tensor-memory quarter = warp)
@@ -510,6 +498,8 @@ k_spmm64(const __grid_constant__ CUtensorMap bmap, int ntasks, int ldb, int row_
             const int s = i % S;
             ok = mbar_wait(bar_full + 8 * s, (i / S) & 1);
             if (!ok) break;
+            // the rows were written by cp.async (generic proxy), the tensor core reads them through the async proxy
+            if (!TMA) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const unsigned st = ring + s * C::STAGE_BYTES;
 #pragma unroll
