@@ -294,6 +294,11 @@ static int check_device_error(tsp_handle *h)
                           flag == 0x20 ? "a tile names a column outside B" : (flag == 0x21 ? "a task lies outside the class's tiles" : "a task writes rows outside C"), flag);
             return TSP_EINVAL;
         }
+        if (flag == 4)
+        {
+            tsp_set_error("the shared memory of an SpMM kernel did not start on the boundary its operand layout needs; nothing was computed");
+            return TSP_ECUDA;
+        }
         tsp_set_error("a bounded wait inside an SpMM kernel ran out (code 0x%x); the result of that launch is incomplete", flag);
         return TSP_ETIMEOUT;
     }

@@ -21,16 +21,7 @@ constexpr int WARPS = 4;
 // (0.347 vs 0.402 ms).  So: 2 stages for 128- and 64-column stripes, 3 for 32-column ones.
 constexpr int ring_stages(int stage_bytes) { return 4608 / stage_bytes < 2 ? 2 : 4608 / stage_bytes; }
 
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
-{
-    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async16s(unsigned smem, const void *gmem)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem), "l"(gmem));
-}
-// The same copy with an L2 eviction policy.  B is re-read many times per product and by every later product, while a
+// 16-byte asynchronous copy global -> shared with an L2 eviction policy.  B is re-read many times per product and by every later product, while a
 // tile of A and a row of C pass through once per product: with B about the size of the L2, letting the one-pass data
 // go first keeps most of B resident (policies made once per thread with createpolicy).
 __device__ __forceinline__ void cp_async16_hint(unsigned smem, const void *gmem, unsigned long long policy)
@@ -56,9 +47,22 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *smem)
+// Shared-memory loads by 32-bit shared address: the operand addresses below are built from a per-lane constant, the
+// slot base and one XOR per load, all in 32-bit arithmetic.
+__device__ __forceinline__ uint4 lds128(unsigned s)
 {
-    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(s));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(unsigned s)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(s));
+    return v;
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, unsigned s)
+{
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
 }
@@ -67,14 +71,8 @@ __device__ __forceinline__ void mma_f16(float *d, unsigned a0, unsigned a1, unsi
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_tf32(float *d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
-{
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// K = 4 form, used by the 8-row kernel: its A operand is two registers that belong to ONE K column, so a lane feeds two
-// MMAs from one 16-byte shared-memory load.
+// K = 4 form of the TF32 MMA: its A operand is two registers that belong to ONE K column, so a lane feeds two MMAs from
+// one 16-byte shared-memory load.
 __device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, unsigned b0)
 {
     asm volatile("mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
@@ -82,44 +80,9 @@ __device__ __forceinline__ void mma_tf32_k4(float *d, unsigned a0, unsigned a1, 
 }
 
 
-#ifndef TSP_SMALL_BULK
-#define TSP_SMALL_BULK 0
-#endif
 // Resident CTAs per SM each instance is compiled for (the register budget of its launch bounds).  The 16-row kernels
-// keep 64 accumulator registers per lane at 128 columns: compiled for 5 or 6 CTAs they spill and measure 16 % / 90 %
-// slower on the 27-point stencil (TF32), and a third ring slot at 4 CTAs is 4 % slower than two -- the kernel is bound
-// by the shared-memory data path (72 % busy) and by issue latency at 16 warps per SM, not by bytes in flight.
+// keep 64 accumulator registers per lane at 128 columns and spill when compiled for 5 or 6 CTAs.
 constexpr int small_ctas(int cls, int ns) { return cls == 2 ? (ns <= 64 ? 8 : 6) : 4; }
-// BULK: the gathered rows and the A tile are fetched by the bulk-copy engine (cp.async.bulk, one copy per row
-// segment, completion on an mbarrier per ring slot) instead of per-lane 16-byte cp.async through the load/store
-// path; rows then sit unswizzled in shared memory with a 16-byte pad per row to keep the operand loads conflict-free.
-// Measured on B200 it is not faster for 512-byte row segments (27-point stencil, TF32, 128 columns: 0.131 ms vs
-// 0.129 ms) and much slower for 128-byte segments (R-MAT scale 20, FP16, 64 columns: 0.72 ms vs 0.45 ms), so it is
-// compiled out by default (-DTSP_SMALL_BULK=1 enables it).
-constexpr bool BULK = TSP_SMALL_BULK != 0;
-constexpr unsigned SMALL_WAIT_LIMIT = 1u << 22;
-
-__device__ __forceinline__ void mbar_init_s(unsigned bar, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_s(unsigned bar, unsigned parity)
-{
-    for (unsigned it = 0; it < SMALL_WAIT_LIMIT; it++)
-    {
-        unsigned done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
 
 template <int PREC, int CLS, int NS>
 struct SmallCfg
@@ -130,20 +93,22 @@ struct SmallCfg
     static constexpr int RB = NS * SZ;                 // bytes of one gathered row segment
     static constexpr int CPR = RB / 16;                // 16-byte chunks per row
     static constexpr int A_BYTES = BM * BN * SZ;       // 512 (16-row) or 256 (8-row)
-    static constexpr int RBS = BULK ? RB + 16 : RB;    // row stride in shared memory
-    static constexpr int B_BYTES = BN * RBS;
+    static constexpr int B_BYTES = BN * RB;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = ring_stages(STAGE_BYTES);
-    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES + (BULK ? 64 : 0);   // + one mbarrier per slot
+    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
     static constexpr int SMEM = WARPS * WARP_BYTES;
+    // the operand addresses are formed as (slot base + per-lane constant) ^ (small multiple of 16): that equals an XOR on the
+    // chunk field of a row (address bits 4-7 at most) alone: slots and the B part inside them start on 256-byte boundaries
+    static_assert(A_BYTES % 256 == 0 && STAGE_BYTES % 256 == 0 && WARP_BYTES % 256 == 0 && RB % 64 == 0, "slot layout");
 };
 
-// chunk position of 16-byte chunk c of row k inside its shared-memory row
+// Gathered row k keeps its 16-byte chunk c at chunk position c ^ key(k) of its shared-memory row, so that the operand
+// loads (several rows, same chunk) and the copies (one row, all chunks) are both free of bank conflicts.
 template <int RB>
-__device__ __forceinline__ int swz(int c, int k)
+__device__ __forceinline__ int swz_key(int k)
 {
-    if (RB >= 128) return c ^ (k & 7);
-    return c ^ ((k >> 1) & 3);
+    return RB >= 128 ? (k & 7) : ((k >> 1) & 3);
 }
 
 // COOP: the four warps of a CTA share ONE (task, stripe): warp w takes tiles w, w+4, ... and the partial blocks are
@@ -156,13 +121,12 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
              const unsigned char *__restrict__ dB, float *__restrict__ dC, int *__restrict__ err, const TspBounds bounds)
 {
     using Cfg = SmallCfg<PREC, CLS, NS>;
-    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES, RBS = Cfg::RBS;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int SZ = Cfg::SZ, BM = Cfg::BM, BN = Cfg::BN, RB = Cfg::RB, CPR = Cfg::CPR, STAGES = Cfg::STAGES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = COOP ? (long long)blockIdx.x : (long long)blockIdx.x * WARPS + warp;
     if (unit >= (long long)ntasks * nstripes) return;   // COOP: never (one CTA per unit)
     const int task = (int)(unit / nstripes), stripe = (int)(unit - (long long)task * nstripes);
-    unsigned char *ring = smem_raw + warp * Cfg::WARP_BYTES;
 
     const uint4 tp = __ldg(task_pack + task);   // {row word, first tile, end tile, -}: one load per task
     const unsigned int trow = tp.x;
@@ -194,156 +158,136 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     for (int i = 0; i < NACC; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
 
     // Per-lane constants of the gather.  Chunk q = it*32 + lane of a tile is 16-byte chunk c = lane % CPR of row
-    // k = it*KPI + lane/CPR (32 % CPR == 0), so the source column offset and the swizzled destination offset of
-    // every copy are loop invariants: one shuffle, one 32x32->64 multiply-add and the copy per 16 bytes.
+    // k = it*KPI + lane/CPR (32 % CPR == 0).  The destination of copy `it` inside the B part of a slot is
+    //   k*RB + ((c ^ key(k)) << 4)  =  (cp_base ^ (key(it*KPI) << 4)) + it*KPI*RB,   cp_base = k0*RB + ((c ^ key(k0)) << 4),
+    // with k0 = lane/CPR (key(it*KPI + k0) = key(it*KPI) ^ key(k0): KPI is a power of two above k0), so a copy costs one
+    // shuffle, one 32x32->64 multiply-add, one XOR with a constant and the copy itself.
     static_assert(32 % CPR == 0 || CPR % 32 == 0, "chunks per row must divide or be a multiple of the warp size");
     constexpr int KPI = CPR <= 32 ? 32 / CPR : 1;          // tile rows covered by one warp-wide copy
     constexpr int ITERS = BN * CPR / 32;
+    static_assert(RB >= 128 || KPI % 2 == 0, "64-byte rows: the swizzle key drops bit 0 of the row");
     const int c_mine = lane % CPR, k_mine = lane / CPR;
     const unsigned char *gsrc = dB + stripe_bytes + (size_t)c_mine * 16;
     const unsigned ldb_b = (unsigned)ldb_bytes;
-    const unsigned ring_s = (unsigned)__cvta_generic_to_shared(ring);
+    const unsigned smem_s = (unsigned)__cvta_generic_to_shared(smem_raw);
+    if (smem_s & 255u)   // the XOR addressing below needs the slots on 256-byte boundaries; same outcome for every thread
+    {
+        if (threadIdx.x == 0) atomicExch(err, 4);
+        return;
+    }
+    const unsigned ring_s = smem_s + (unsigned)warp * Cfg::WARP_BYTES;
+    const unsigned cp_base = Cfg::A_BYTES + (unsigned)k_mine * RB + ((unsigned)(c_mine ^ swz_key<RB>(k_mine)) << 4);
     const unsigned char *a_src = tile_val + (size_t)t0 * Cfg::A_BYTES + lane * 16;
     const int *idx_ptr = tile_colidx + (size_t)t0 * BN + lane;
     // column index of tile row `lane` for the tile that will be issued next
     int idx_next = (nt > 0 && lane < BN) ? __ldg(idx_ptr) : 0;
     if (TSP_CHECKED && (unsigned)idx_next >= (unsigned)bounds.colA) { atomicExch(err, 0x20); idx_next = 0; }
 
-    const unsigned bars = ring_s + STAGES * Cfg::STAGE_BYTES;
-    if (BULK)
-    {
-        if (lane == 0)
-        {
-            for (int q = 0; q < STAGES; q++) mbar_init_s(bars + 8 * q, 1);
-            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        }
-        __syncwarp();
-    }
-    const unsigned char *a_tile = tile_val + (size_t)t0 * Cfg::A_BYTES;
-    const unsigned char *grow = dB + stripe_bytes;
-
     const unsigned long long pol_once = policy_evict_first(), pol_keep = policy_evict_last();
     auto issue = [&](int i) {
         const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
-        if (BULK)
-        {
-            // lane k < BN fetches gathered row k (RB contiguous bytes of B), lane BN the A tile; lane 0 arms the slot
-            const unsigned bar = bars + 8 * (i % STAGES);
-            if (lane == 0) mbar_expect_tx(bar, Cfg::A_BYTES + BN * RB);
-            if (lane < BN) bulk_g2s(st + Cfg::A_BYTES + lane * RBS, grow + (unsigned long long)(unsigned)idx_next * ldb_b, RB, bar);
-            else if (lane == BN) bulk_g2s(st, a_tile, Cfg::A_BYTES, bar);
-            a_tile += TS * Cfg::A_BYTES;
-        }
-        else
-        {
-            if (lane * 16 < Cfg::A_BYTES) cp_async16_hint(st + lane * 16, a_src, pol_once);
-            a_src += TS * Cfg::A_BYTES;
-            const int idx_mine = idx_next;
+        if (lane * 16 < Cfg::A_BYTES) cp_async16_hint(st + lane * 16, a_src, pol_once);
+        a_src += TS * Cfg::A_BYTES;
+        const int idx_mine = idx_next;
+        const unsigned dst = st + cp_base;
 #pragma unroll
-            for (int it = 0; it < ITERS; it++)
-            {
-                const int k = it * KPI + k_mine;
-                const int col = __shfl_sync(0xffffffffu, idx_mine, k);
-                cp_async16_hint(st + Cfg::A_BYTES + k * RB + (swz<RB>(c_mine, k) << 4), gsrc + (unsigned long long)(unsigned)col * ldb_b, pol_keep);
-            }
+        for (int it = 0; it < ITERS; it++)
+        {
+            const int col = __shfl_sync(0xffffffffu, idx_mine, it * KPI + k_mine);
+            cp_async16_hint((dst ^ ((unsigned)swz_key<RB>(it * KPI) << 4)) + (unsigned)(it * KPI * RB), gsrc + (unsigned long long)(unsigned)col * ldb_b, pol_keep);
         }
         idx_ptr += TS * BN;
         if (i + 1 < nt && lane < BN) idx_next = __ldg(idx_ptr);
         if (TSP_CHECKED && (unsigned)idx_next >= (unsigned)bounds.colA) { atomicExch(err, 0x20); idx_next = 0; }
     };
-    // byte offset of 16-byte chunk `chunk` of gathered row k inside the B part of a slot
-    auto boff = [&](int k, int chunk) -> int { return BULK ? k * RBS + chunk * 16 : k * RB + swz<RB>(chunk, k) * 16; };
 
-    bool ok = true;
+    // Per-lane constants of the operand loads: a lane reads chunk c0 + n*step (n = 0, 1, ...) of tile row kx (and of row
+    // kx + 4 in the TF32 forms), i.e. the bytes at (slot + op_x) ^ (n*step << 4) -- one XOR with a constant per load.
+    //   FP16 16-row (ldmatrix.x4.trans): row ((lane>>3)&1)*8 + (lane&7), chunks nb + (lane>>4), nb = 0, 2, ...
+    //   FP16 8-row  (ldmatrix.x4.trans): row (lane>>4)*8 + (lane&7),     chunks 2*mb + ((lane>>3)&1)
+    //   TF32: lane group g = lane/4 owns the W = NS/8 consecutive output columns g*W.. (W/4 chunks), row lane%4 (+4)
+    unsigned op_x, op_y = 0;
+    if constexpr (PREC == 0)
+    {
+        const int kx = CLS == 1 ? ((lane >> 3) & 1) * 8 + (lane & 7) : (lane >> 4) * 8 + (lane & 7);
+        const int c0 = CLS == 1 ? (lane >> 4) : ((lane >> 3) & 1);
+        op_x = Cfg::A_BYTES + (unsigned)kx * RB + ((unsigned)(c0 ^ swz_key<RB>(kx)) << 4);
+    }
+    else
+    {
+        const int kx = lane & 3, c0 = (lane >> 2) * (NS / 32);
+        op_x = Cfg::A_BYTES + (unsigned)kx * RB + ((unsigned)(c0 ^ swz_key<RB>(kx)) << 4);
+        op_y = Cfg::A_BYTES + (unsigned)(kx + 4) * RB + ((unsigned)(c0 ^ swz_key<RB>(kx + 4)) << 4);
+    }
+
     for (int i = 0; i < STAGES - 1; i++)
     {
         if (i < nt) issue(i);
-        if (!BULK) cp_async_commit();
+        cp_async_commit();
     }
     for (int i = 0; i < nt; i++)
     {
         if (i + STAGES - 1 < nt) issue(i + STAGES - 1);
-        if (BULK)
-        {
-            ok = __all_sync(0xffffffffu, mbar_wait_s(bars + 8 * (i % STAGES), (i / STAGES) & 1));
-            if (!ok)
-            {
-                // give the copies still in flight one more bounded chance to land, report, and stop
-                if (lane == 0) atomicExch(err, 2);
-                for (int q = i; q < nt && q < i + STAGES; q++) mbar_wait_s(bars + 8 * (q % STAGES), (q / STAGES) & 1);
-                break;
-            }
-        }
-        else
-        {
-            cp_async_commit();
-            cp_async_wait<STAGES - 1>();
-            __syncwarp();
-        }
-        const unsigned char *st = ring + (i % STAGES) * Cfg::STAGE_BYTES;
-        const unsigned char *sb = st + Cfg::A_BYTES;
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
         if constexpr (CLS == 1 && PREC == 0)
         {
-            const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
-            const int k = ((lane >> 3) & 1) * 8 + (lane & 7);
+            const uint4 a = lds128(st + lane * 16);
 #pragma unroll
             for (int nb = 0; nb < NS / 8; nb += 2)
             {
-                const int chunk = nb + (lane >> 4);
                 unsigned r0, r1, r2, r3;
-                ldmatrix_x4_trans(r0, r1, r2, r3, sb + boff(k, chunk));
+                ldmatrix_x4_trans(r0, r1, r2, r3, (st + op_x) ^ (unsigned)(nb << 4));
                 mma_f16(acc[nb], a.x, a.y, a.z, a.w, r0, r1);
                 mma_f16(acc[nb + 1], a.x, a.y, a.z, a.w, r2, r3);
             }
         }
-        else if constexpr (CLS == 1 && PREC == 1)
-        {
-            // TF32 has no ldmatrix path, so the output columns of the MMAs are permuted instead: lane group
-            // g = lane/4 owns the W = NS/8 consecutive columns g*W.., and n-block nb uses column g*W + nb of
-            // every group.  A lane then reads its B operands with 16-byte loads (W/4 per K row).
-            const uint4 a = *reinterpret_cast<const uint4 *>(st + lane * 16);
-            constexpr int W = NS / 8;
-            const int k = lane & 3, g = lane >> 2;
-            // one K = 8 MMA per n-block: tile rows 0-3 (x) and 4-7 (y) of the lane's column group (5% faster on B200
-            // than two K = 4 MMAs here; the 8-row form below measures the same either way)
-#pragma unroll
-            for (int j = 0; j < W / 4; j++)
-            {
-                const int chunk = g * (W / 4) + j;
-                const uint4 x = *reinterpret_cast<const uint4 *>(sb + boff(k, chunk));
-                const uint4 y = *reinterpret_cast<const uint4 *>(sb + boff(k + 4, chunk));
-                mma_tf32(acc[4 * j], a.x, a.y, a.z, a.w, x.x, y.x); mma_tf32(acc[4 * j + 1], a.x, a.y, a.z, a.w, x.y, y.y);
-                mma_tf32(acc[4 * j + 2], a.x, a.y, a.z, a.w, x.z, y.z); mma_tf32(acc[4 * j + 3], a.x, a.y, a.z, a.w, x.w, y.w);
-            }
-        }
         else if constexpr (CLS == 2 && PREC == 0)
         {
-            const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
-            const int k = (lane >> 4) * 8 + (lane & 7);
+            const uint2 b = lds64(st + lane * 8);
 #pragma unroll
             for (int mb = 0; mb < NS / 16; mb++)
             {
-                const int chunk = mb * 2 + ((lane >> 3) & 1);
                 unsigned a0, a1, a2, a3;
-                ldmatrix_x4_trans(a0, a1, a2, a3, sb + boff(k, chunk));
+                ldmatrix_x4_trans(a0, a1, a2, a3, (st + op_x) ^ (unsigned)(mb << 5));
                 mma_f16(acc[mb], a0, a1, a2, a3, b.x, b.y);
+            }
+        }
+        else if constexpr (CLS == 1)
+        {
+            // TF32 has no ldmatrix path, so the output columns of the MMAs are permuted instead: lane group g = lane/4
+            // owns the W = NS/8 consecutive columns g*W.., read with 16-byte loads.  The product is formed transposed
+            // (the gathered rows are the m16 x k4 operand, the tile the k4 x n8 operand) once per half of the tile's rows,
+            // so that the two registers of an operand are neighbours of ONE load: the 16 x 8 x 8 form needs its two B
+            // registers from two different loads and pays two register moves per MMA for it.  The fragment-order tile
+            // is exactly the four k4 x n8 operands: a.x rows 0-7 / columns 0-3, a.y rows 8-15 / columns 0-3, a.z and a.w
+            // the same rows for columns 4-7.  Accumulators 0 .. W/2-1: rows 0-7, W/2 .. W-1: rows 8-15.
+            const uint4 a = lds128(st + lane * 16);
+            constexpr int H = NS / 16;
+#pragma unroll
+            for (int j = 0; j < NS / 32; j++)
+            {
+                const uint4 x = lds128((st + op_x) ^ (unsigned)(j << 4));
+                const uint4 y = lds128((st + op_y) ^ (unsigned)(j << 4));
+                mma_tf32_k4(acc[2 * j], x.x, x.y, a.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, a.x);
+                mma_tf32_k4(acc[H + 2 * j], x.x, x.y, a.y); mma_tf32_k4(acc[H + 2 * j + 1], x.z, x.w, a.y);
+                mma_tf32_k4(acc[2 * j], y.x, y.y, a.z); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, a.z);
+                mma_tf32_k4(acc[H + 2 * j], y.x, y.y, a.w); mma_tf32_k4(acc[H + 2 * j + 1], y.z, y.w, a.w);
             }
         }
         else
         {
-            // same column permutation as the 16-row TF32 kernel: lane group g owns columns g*W .. g*W+W-1 and
-            // MMA mb takes column g*W + 2*mb for its row m = g and g*W + 2*mb + 1 for its row m + 8
-            const uint2 b = *reinterpret_cast<const uint2 *>(st + lane * 8);
-            constexpr int W = NS / 8;
-            const int k = lane & 3, g = lane >> 2;
-            // two K = 4 MMAs per 16 columns: tile rows 0-3 with b.x, rows 4-7 with b.y; one 16-byte load of a
-            // gathered row yields the A operands (columns 2*mb, 2*mb+1 of the lane's group) of two MMAs
+            // same column permutation: lane group g owns columns g*W .. g*W+W-1 and MMA mb takes column g*W + 2*mb for
+            // its row m = g and g*W + 2*mb + 1 for its row m + 8.  Two K = 4 MMAs per 16 columns: tile rows 0-3 with
+            // b.x, rows 4-7 with b.y; one 16-byte load of a gathered row yields the operands of two MMAs
+            const uint2 b = lds64(st + lane * 8);
 #pragma unroll
-            for (int j = 0; j < W / 4; j++)
+            for (int j = 0; j < NS / 32; j++)
             {
-                const int chunk = g * (W / 4) + j;
-                const uint4 x = *reinterpret_cast<const uint4 *>(sb + boff(k, chunk));
-                const uint4 y = *reinterpret_cast<const uint4 *>(sb + boff(k + 4, chunk));
+                const uint4 x = lds128((st + op_x) ^ (unsigned)(j << 4));
+                const uint4 y = lds128((st + op_y) ^ (unsigned)(j << 4));
                 mma_tf32_k4(acc[2 * j], x.x, x.y, b.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, b.x);
                 mma_tf32_k4(acc[2 * j], y.x, y.y, b.y); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, b.y);
             }
@@ -351,11 +295,9 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         __syncwarp();
     }
 
-    if (!ok) return;
     if constexpr (COOP)
     {
         // warps 1-3 hand their partial block to warp 0 through the (now idle) rings, lane-major
-        static_assert(!BULK, "the cooperative form reuses the rings, which hold mbarriers in the bulk-copy variant");
         static_assert((WARPS - 1) * 32 * NACC * 16 <= Cfg::SMEM, "partial blocks must fit the rings");
         float4 *red = reinterpret_cast<float4 *>(smem_raw);
         __syncthreads();   // every warp is done reading its ring
@@ -379,23 +321,24 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
     // epilogue.  ldc == ldb (upstream uses the padded width as the row stride of both, src/main.cu:173)
     const size_t ldc = (size_t)ldb;
     float *cbase = dC + (size_t)first_row * ldc + (size_t)stripe * NS;
-    if constexpr (CLS == 1 && PREC == 1)
+    if constexpr (PREC == 1)
     {
-        // permuted columns: accumulator (row, n') of n-block nb is C[row][n'*W + nb], n' = (lane%4)*2 + {0,1}
-        constexpr int W = NS / 8;
-        const int r = lane >> 2;
+        // transposed blocks with permuted columns: accumulator (m, n) of MMA mb of row half h is
+        // C[row 8*h + n][g*W + 2*mb + (m >= 8)]
+        constexpr int W = NS / 8, HALVES = CLS == 1 ? 2 : 1;
+        const int g = lane >> 2, n = (lane & 3) * 2;
 #pragma unroll
-        for (int half = 0; half < 2; half++)
+        for (int h = 0; h < HALVES; h++)
 #pragma unroll
             for (int j = 0; j < 2; j++)
             {
-                float *p = cbase + (size_t)(r + 8 * half) * ldc + ((lane & 3) * 2 + j) * W;
+                float *p = cbase + (size_t)(8 * h + n + j) * ldc + g * W;
 #pragma unroll
-                for (int q = 0; q < W; q += 4)
+                for (int q = 0; q < W / 2; q += 2)
                 {
-                    const float v0 = acc[q][half * 2 + j], v1 = acc[q + 1][half * 2 + j], v2 = acc[q + 2][half * 2 + j], v3 = acc[q + 3][half * 2 + j];
-                    if (split) { atomicAdd(p + q, v0); atomicAdd(p + q + 1, v1); atomicAdd(p + q + 2, v2); atomicAdd(p + q + 3, v3); }
-                    else store_streaming(reinterpret_cast<float4 *>(p + q), make_float4(v0, v1, v2, v3));
+                    const float v0 = acc[h * (W / 2) + q][j], v1 = acc[h * (W / 2) + q][2 + j], v2 = acc[h * (W / 2) + q + 1][j], v3 = acc[h * (W / 2) + q + 1][2 + j];
+                    if (split) { atomicAdd(p + 2 * q, v0); atomicAdd(p + 2 * q + 1, v1); atomicAdd(p + 2 * q + 2, v2); atomicAdd(p + 2 * q + 3, v3); }
+                    else store_streaming(reinterpret_cast<float4 *>(p + 2 * q), make_float4(v0, v1, v2, v3));
                 }
             }
     }
@@ -415,24 +358,6 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             {
                 store_streaming(reinterpret_cast<float2 *>(p0), make_float2(acc[nb][0], acc[nb][1]));
                 store_streaming(reinterpret_cast<float2 *>(p1), make_float2(acc[nb][2], acc[nb][3]));
-            }
-        }
-    }
-    else if constexpr (PREC == 1)
-    {
-        // transposed block with permuted columns: accumulator (m, n) of MMA mb is C[row n][g*W + 2*mb + (m >= 8)]
-        constexpr int W = NS / 8;
-        const int g = lane >> 2, n = (lane & 3) * 2;
-#pragma unroll
-        for (int j = 0; j < 2; j++)
-        {
-            float *p = cbase + (size_t)(n + j) * ldc + g * W;
-#pragma unroll
-            for (int q = 0; q < W / 2; q += 2)
-            {
-                const float v0 = acc[q][j], v1 = acc[q][2 + j], v2 = acc[q + 1][j], v3 = acc[q + 1][2 + j];
-                if (split) { atomicAdd(p + 2 * q, v0); atomicAdd(p + 2 * q + 1, v1); atomicAdd(p + 2 * q + 2, v2); atomicAdd(p + 2 * q + 3, v3); }
-                else store_streaming(reinterpret_cast<float4 *>(p + 2 * q), make_float4(v0, v1, v2, v3));
             }
         }
     }
