@@ -60,3 +60,10 @@ def test_library_table_is_within_the_accepted_range():
                 w = api.atom_weight(prec, cls, cb)
                 assert cal.LO * 0.999 <= w <= cal.HI * 1.001, (prec, cls, cb, w)
             assert api.atom_weight(prec, cls, 64) == api.atom_weight(prec, cls, 256)   # one row for every width above 32
+
+
+@pytest.mark.gpu
+def test_calibration_leg_runs_on_the_gpu():
+    """One small (precision, class, width) case end to end: conversion, every candidate threshold scheduled and timed, fit."""
+    lam, raw, r2, n = cal.fit_case(1, 1, 128, iters=5, panels=256, tiles_per_panel=64)
+    assert cal.LO <= lam <= cal.HI and n >= 3 and np.isfinite(raw) and np.isfinite(r2)
