@@ -107,7 +107,8 @@ def sweep(out_path: str, iters: int, cases=None, candidates=None):
                 if key not in seen:
                     dC = torch.empty((m.c_rows(), cb), dtype=torch.float32, device="cuda")
                     m.tune(dB, dC, cb)
-                    seen[key] = m.time(dB, dC, cb, iters)
+                    # best of three loops: one disturbed loop (another tenant of the machine, a clock event) must not reach the fit
+                    seen[key] = min(m.time(dB, dC, cb, iters) for _ in range(3))
                     del dC
                 times.append(seen[key])
             times = [t if t is not None else times[DEFAULT_LEAF] for t in times]
