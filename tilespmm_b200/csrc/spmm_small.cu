@@ -220,40 +220,66 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
         op_y = Cfg::A_BYTES + (unsigned)(kx + 4) * RB + ((unsigned)(c0 ^ swz_key<RB>(kx + 4)) << 4);
     }
 
-    for (int i = 0; i < STAGES - 1; i++)
+    // The slot of a tile is given back as soon as its last operand is in registers: the MMAs of all but the last step of
+    // the tile run from loads issued as they go, then the operands of the last step are loaded, the tile STAGES ahead is
+    // requested into the slot, and the last MMAs run while that request is already in flight -- all STAGES slots of a warp
+    // are in flight except during the loads of one.  (Deferring more steps costs registers: two steps measure 3 % slower
+    // on the 27-point stencil, all four spill and run 1.7x slower.)
+    for (int i = 0; i < STAGES; i++)
     {
         if (i < nt) issue(i);
         cp_async_commit();
     }
     for (int i = 0; i < nt; i++)
     {
-        if (i + STAGES - 1 < nt) issue(i + STAGES - 1);
-        cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncwarp();
         const unsigned st = ring_s + (unsigned)(i % STAGES) * Cfg::STAGE_BYTES;
+        auto release = [&]() {
+            __syncwarp();   // every lane has its operands: the slot may be overwritten
+            if (i + STAGES < nt) issue(i + STAGES);
+            cp_async_commit();
+        };
         if constexpr (CLS == 1 && PREC == 0)
         {
+            constexpr int NP = NS / 16, D = 1;   // pairs of n-blocks; deferred pairs
             const uint4 a = lds128(st + lane * 16);
 #pragma unroll
-            for (int nb = 0; nb < NS / 8; nb += 2)
+            for (int p = 0; p < NP - D; p++)
             {
                 unsigned r0, r1, r2, r3;
-                ldmatrix_x4_trans(r0, r1, r2, r3, (st + op_x) ^ (unsigned)(nb << 4));
-                mma_f16(acc[nb], a.x, a.y, a.z, a.w, r0, r1);
-                mma_f16(acc[nb + 1], a.x, a.y, a.z, a.w, r2, r3);
+                ldmatrix_x4_trans(r0, r1, r2, r3, (st + op_x) ^ (unsigned)(p << 5));
+                mma_f16(acc[2 * p], a.x, a.y, a.z, a.w, r0, r1);
+                mma_f16(acc[2 * p + 1], a.x, a.y, a.z, a.w, r2, r3);
+            }
+            unsigned r[D][4];
+#pragma unroll
+            for (int q = 0; q < D; q++) ldmatrix_x4_trans(r[q][0], r[q][1], r[q][2], r[q][3], (st + op_x) ^ (unsigned)((NP - D + q) << 5));
+            release();
+#pragma unroll
+            for (int q = 0; q < D; q++)
+            {
+                mma_f16(acc[2 * (NP - D + q)], a.x, a.y, a.z, a.w, r[q][0], r[q][1]);
+                mma_f16(acc[2 * (NP - D + q) + 1], a.x, a.y, a.z, a.w, r[q][2], r[q][3]);
             }
         }
         else if constexpr (CLS == 2 && PREC == 0)
         {
+            constexpr int MB = NS / 16, D = 1;
             const uint2 b = lds64(st + lane * 8);
 #pragma unroll
-            for (int mb = 0; mb < NS / 16; mb++)
+            for (int mb = 0; mb < MB - D; mb++)
             {
                 unsigned a0, a1, a2, a3;
                 ldmatrix_x4_trans(a0, a1, a2, a3, (st + op_x) ^ (unsigned)(mb << 5));
                 mma_f16(acc[mb], a0, a1, a2, a3, b.x, b.y);
             }
+            unsigned r[D][4];
+#pragma unroll
+            for (int q = 0; q < D; q++) ldmatrix_x4_trans(r[q][0], r[q][1], r[q][2], r[q][3], (st + op_x) ^ (unsigned)((MB - D + q) << 5));
+            release();
+#pragma unroll
+            for (int q = 0; q < D; q++) mma_f16(acc[MB - D + q], r[q][0], r[q][1], r[q][2], r[q][3], b.x, b.y);
         }
         else if constexpr (CLS == 1)
         {
@@ -264,35 +290,43 @@ k_spmm_small(int ntasks, int nstripes, int ldb /* elements */, int row_begin, co
             // registers from two different loads and pays two register moves per MMA for it.  The fragment-order tile
             // is exactly the four k4 x n8 operands: a.x rows 0-7 / columns 0-3, a.y rows 8-15 / columns 0-3, a.z and a.w
             // the same rows for columns 4-7.  Accumulators 0 .. W/2-1: rows 0-7, W/2 .. W-1: rows 8-15.
+            constexpr int NJ = NS / 32, D = 1, H = NS / 16;
             const uint4 a = lds128(st + lane * 16);
-            constexpr int H = NS / 16;
-#pragma unroll
-            for (int j = 0; j < NS / 32; j++)
-            {
-                const uint4 x = lds128((st + op_x) ^ (unsigned)(j << 4));
-                const uint4 y = lds128((st + op_y) ^ (unsigned)(j << 4));
+            auto mmas = [&](int j, const uint4 &x, const uint4 &y) {
                 mma_tf32_k4(acc[2 * j], x.x, x.y, a.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, a.x);
                 mma_tf32_k4(acc[H + 2 * j], x.x, x.y, a.y); mma_tf32_k4(acc[H + 2 * j + 1], x.z, x.w, a.y);
                 mma_tf32_k4(acc[2 * j], y.x, y.y, a.z); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, a.z);
                 mma_tf32_k4(acc[H + 2 * j], y.x, y.y, a.w); mma_tf32_k4(acc[H + 2 * j + 1], y.z, y.w, a.w);
-            }
+            };
+#pragma unroll
+            for (int j = 0; j < NJ - D; j++) mmas(j, lds128((st + op_x) ^ (unsigned)(j << 4)), lds128((st + op_y) ^ (unsigned)(j << 4)));
+            uint4 xs[D], ys[D];
+#pragma unroll
+            for (int q = 0; q < D; q++) { xs[q] = lds128((st + op_x) ^ (unsigned)((NJ - D + q) << 4)); ys[q] = lds128((st + op_y) ^ (unsigned)((NJ - D + q) << 4)); }
+            release();
+#pragma unroll
+            for (int q = 0; q < D; q++) mmas(NJ - D + q, xs[q], ys[q]);
         }
         else
         {
             // same column permutation: lane group g owns columns g*W .. g*W+W-1 and MMA mb takes column g*W + 2*mb for
             // its row m = g and g*W + 2*mb + 1 for its row m + 8.  Two K = 4 MMAs per 16 columns: tile rows 0-3 with
             // b.x, rows 4-7 with b.y; one 16-byte load of a gathered row yields the operands of two MMAs
+            constexpr int NJ = NS / 32, D = 1;
             const uint2 b = lds64(st + lane * 8);
-#pragma unroll
-            for (int j = 0; j < NS / 32; j++)
-            {
-                const uint4 x = lds128((st + op_x) ^ (unsigned)(j << 4));
-                const uint4 y = lds128((st + op_y) ^ (unsigned)(j << 4));
+            auto mmas = [&](int j, const uint4 &x, const uint4 &y) {
                 mma_tf32_k4(acc[2 * j], x.x, x.y, b.x); mma_tf32_k4(acc[2 * j + 1], x.z, x.w, b.x);
                 mma_tf32_k4(acc[2 * j], y.x, y.y, b.y); mma_tf32_k4(acc[2 * j + 1], y.z, y.w, b.y);
-            }
+            };
+#pragma unroll
+            for (int j = 0; j < NJ - D; j++) mmas(j, lds128((st + op_x) ^ (unsigned)(j << 4)), lds128((st + op_y) ^ (unsigned)(j << 4)));
+            uint4 xs[D], ys[D];
+#pragma unroll
+            for (int q = 0; q < D; q++) { xs[q] = lds128((st + op_x) ^ (unsigned)((NJ - D + q) << 4)); ys[q] = lds128((st + op_y) ^ (unsigned)((NJ - D + q) << 4)); }
+            release();
+#pragma unroll
+            for (int q = 0; q < D; q++) mmas(NJ - D + q, xs[q], ys[q]);
         }
-        __syncwarp();
     }
 
     if constexpr (COOP)
