@@ -2,8 +2,8 @@
 //
 // They replace upstream stir_spmm_cuda_kernel_v16*/v8* (src/tilespmm_cuda.h:12-1023) and the launch switches
 // (src/tilespmm_cuda.h:1634-1708).  Differences that matter on B200:
-//   * one warp owns one (task, column stripe) and keeps a 2- to 6-deep ring of gathered B rows in flight
-//     (upstream: depth 1 for 16-row tiles, none for 8-row tiles) at 16-24 resident warps per SM;
+//   * one warp owns one (task, column stripe) and keeps a 2- or 3-deep ring of gathered B rows in flight
+//     (upstream: depth 1 for 16-row tiles, none for 8-row tiles) at 16-32 resident warps per SM;
 //   * a stripe is up to 128 columns wide (upstream: 64), so the A tile and the column indices are read
 //     once per 128 columns and a gathered row segment is up to 512 contiguous bytes;
 //   * every global access is a 16-byte cp.async (B rows, A tile) or a full 32-byte sector store (C);
