@@ -46,9 +46,9 @@ C5_CPU_SAMPLE = 8          # the CPU arm multiplies every 8th block of 1024 rows
 # same tiling as the capture (`tiles` must match), otherwise the roofline falls back to the compulsory bytes.
 TRAFFIC = {
     ("c2", 2): {"bytes": 363.8e6, "tiles": 376872, "source": "profiles/c2_spmm_8row_tf32.md"},
-    ("c2", 0): {"bytes": 281.6e6, "tiles": 144400, "source": "profiles/c2_spmm_64row_tf32_tcgen05.md"},
-    ("c3", 2): {"bytes": 1020.0e6, "tiles": 1849624, "source": "profiles/c3_spmm_8row_fp16.md"},
-    ("c4", 2): {"bytes": 2210.0e6, "tiles": 235936, "source": "profiles/c4_spmm_8row_64row_tf32.md"},
+    ("c2", 0): {"bytes": 281.4e6, "tiles": 144400, "source": "profiles/c2_spmm_64row_tf32_tcgen05.md"},
+    ("c3", 2): {"bytes": 1019.6e6, "tiles": 1849624, "source": "profiles/c3_spmm_8row_fp16.md"},
+    ("c4", 2): {"bytes": 2210.4e6, "tiles": 235936, "source": "profiles/c4_spmm_8row_64row_tf32.md"},
 }
 
 
