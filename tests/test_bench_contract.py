@@ -34,3 +34,14 @@ def test_workload_rule():
     for key, rec in bench.TRAFFIC.items():
         assert os.path.exists(os.path.join(ROOT, rec["source"])), rec["source"]
         assert rec["bytes"] > 0 and rec["tiles"] > 0
+
+
+def test_every_profile_summary_names_its_command():
+    """profiles/ holds text summaries only, each with the command that produced it (committed files only)."""
+    pdir = os.path.join(ROOT, "profiles")
+    names = sorted(os.listdir(pdir))
+    assert names and all(n.endswith((".md", ".txt")) for n in names), names
+    for n in names:
+        text = open(os.path.join(pdir, n)).read()
+        assert "Command" in text and ("bench.py" in text), n
+        assert "_work" not in text and "gpurun" not in text, n
